@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the docc library-node hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload softmax|gemm_f64|conv_f32|conv_bf16|attention|attention_causal|block_f32|block_bf16]
+                    [--no-extras]
+
+Prints ONE JSON line. The headline workload (default) is BASELINE config 2: row softmax over a
+fp32 [8192, 4096] tensor, reported as algorithmic HBM GB/s (one read + one write of the tensor).
+A "step" is one pass of the node over one batch of synthetic input. With --gpus N every rank
+processes its own batch (weak scaling, no data-path collective for softmax; the batch-sharded
+contraction workloads end with one NCCL all-gather of the output shards).
+
+``--impl reference`` times the CPU restatement of the reference's own expansion of the node
+(oracle/, OpenMP over the outermost map as docc's openmp target schedules it) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, sm_max, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------------
+# workloads: each returns a dict with a `step()` closure over device-resident inputs, the algorithmic
+# work per step and the roofline that bounds it
+# ------------------------------------------------------------------------------------------------------
+def make_workload(name, torch, ops, rank, world):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = measured_peaks()
+    g = torch.Generator(device="cpu")
+
+    if name == "softmax":
+        rows, cols = 8192, 4096
+        g.manual_seed(1 + rank)
+        n_buf = 4  # 4 x (134 MB in + 134 MB out): consecutive steps never find their input in the 126 MB L2
+        xs = [(3 * torch.randn(rows, cols, generator=g)).to(dev) for _ in range(n_buf)]
+        ys = [torch.empty_like(x) for x in xs]
+        shape = ops._arr((rows, cols))
+        axes = ops._arr((1,))
+        state = {"i": 0}
+
+        def step():
+            i = state["i"] % n_buf
+            state["i"] += 1
+            ops.call("docc_b200_softmax", ord("s"), 2, shape, 1, axes, ops._ptr(xs[i]), ops._ptr(ys[i]), 0)
+
+        units = 2 * rows * cols * 4  # bytes: one read + one write
+        return dict(step=step, units=units, unit="GB/s", scale=1e-9, metric="softmax_hbm_gbs", dtype="f32",
+                    bound="hbm", peak=peaks["hbm_gbs"], launches_per_step=1,
+                    config={"workload": "softmax fp32 [8192,4096] axis=-1 (BASELINE config 2)", "rows_per_gpu": rows,
+                            "cols": cols, "l2": "inputs larger than L2 and rotated over 4 buffer pairs"},
+                    host_inputs=lambda: [(3 * torch.randn(rows, cols, generator=g))], kind="softmax",
+                    h2d=rows * cols * 4, d2h=rows * cols * 4)
+
+    if name == "gemm_f64":
+        rs = np.random.RandomState(0)
+        a = torch.from_numpy(rs.rand(1000, 1000)).to(dev)
+        b = torch.from_numpy(rs.rand(1000, 1000)).to(dev)
+        c = torch.empty(1000, 1000, dtype=torch.float64, device=dev)
+
+        def step():
+            ops.gemm(a, b, c)
+
+        return dict(step=step, units=2 * 1000 ** 3, unit="TFLOP/s", scale=1e-12, metric="gemm_fp64_tflops", dtype="f64",
+                    bound="tensor", peak=None, launches_per_step=1,
+                    config={"workload": "GEMM fp64 1000x1000x1000 (BASELINE config 1)", "l2": "flushed between steps"},
+                    flush=True, kind="gemm", replicas_only=True)
+
+    if name in ("conv_f32", "conv_bf16"):
+        n_total = 32
+        n_local = n_total // world if world > 1 else n_total
+        g.manual_seed(2)
+        x = torch.randn(n_total, 64, 56, 56, generator=g)[rank * n_local:(rank + 1) * n_local]
+        w = torch.nn.init.kaiming_normal_(torch.empty(128, 64, 3, 3), generator=g)
+        bias = torch.zeros(128)
+        if name == "conv_bf16":
+            x, w = x.bfloat16(), w.bfloat16()
+        x, w, bias = x.to(dev), w.to(dev), bias.to(dev)
+        pads = [1, 1, 1, 1]
+
+        def step():
+            return ops.conv(x, w, bias, pads=pads)
+
+        flops = 2 * n_local * 128 * 56 * 56 * 64 * 9
+        return dict(step=step, units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops",
+                    dtype="bf16" if name == "conv_bf16" else "f32(split-bf16x3)", bound="tensor",
+                    peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None,
+                    config={"workload": f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)",
+                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv", gather=True)
+
+    if name in ("attention", "attention_causal"):
+        causal = name.endswith("causal")
+        bh_total = 8
+        b_local = bh_total // world if world > 1 else bh_total
+        g.manual_seed(3)
+        q, k, v = (torch.randn(bh_total, 16, 2048, 128, generator=g)[rank * b_local:(rank + 1) * b_local].bfloat16().to(dev)
+                   for _ in range(3))
+
+        def step():
+            return ops.attention(q, k, v, causal=causal)
+
+        flops = 4 * b_local * 16 * 2048 * 2048 * 128 // (2 if causal else 1)
+        return dict(step=step, units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops", dtype="bf16",
+                    bound="tensor", peak=peaks["bf16_tflops"], launches_per_step=1,
+                    config={"workload": f"attention bf16 [8,16,2048,128] causal={causal} (BASELINE config 4)",
+                            "batch_per_gpu": b_local, "l2": "flushed between steps"}, flush=True, kind="attention",
+                    gather=True)
+
+    if name in ("block_f32", "block_bf16"):
+        bf = name.endswith("bf16")
+        b_total = 32
+        b_local = b_total // world if world > 1 else b_total
+        d, heads, dff, seq = 1024, 16, 4096, 512
+        torch.manual_seed(4)
+        p = {"ln1_g": torch.ones(d), "ln1_b": torch.zeros(d), "ln2_g": torch.ones(d), "ln2_b": torch.zeros(d)}
+        for nm, shp in (("w_qkv", (3 * d, d)), ("w_o", (d, d)), ("w_1", (dff, d)), ("w_2", (d, dff))):
+            p[nm] = torch.nn.init.xavier_uniform_(torch.empty(*shp))
+        for nm, n in (("b_qkv", 3 * d), ("b_o", d), ("b_1", dff), ("b_2", d)):
+            p[nm] = torch.zeros(n)
+        x = torch.randn(b_total, seq, d)[rank * b_local:(rank + 1) * b_local]
+        small = ("ln1_g", "ln1_b", "ln2_g", "ln2_b", "b_qkv", "b_o", "b_1", "b_2")
+        pd = {k_: (v_.to(dev) if (k_ in small or not bf) else v_.bfloat16().to(dev)) for k_, v_ in p.items()}
+        x = (x.bfloat16() if bf else x).to(dev)
+
+        def step():
+            return ops.transformer_block(x, pd, heads)
+
+        T = b_local * seq
+        flops = 2 * T * d * (3 * d + d + 2 * dff) + 4 * b_local * heads * seq * seq * (d // heads)
+        return dict(step=step, units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops",
+                    dtype="bf16" if bf else "f32(split-bf16x3)", bound="tensor",
+                    peak=peaks["bf16_tflops_sustained"] / (1 if bf else 3), launches_per_step=None,
+                    config={"workload": f"pre-LN encoder block {'bf16' if bf else 'fp32'} d1024 h16 ff4096 [32,512,1024] "
+                                        "(BASELINE config 5)", "batch_per_gpu": b_local, "l2": "flushed between steps"},
+                    flush=True, kind="block", gather=True)
+
+    raise SystemExit(f"unknown workload {name}")
+
+
+def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clocks=False):
+    """Device-timed loop: W warm-ups, then K steps bracketed by barrier + synchronize, max over ranks."""
+    dev_index = torch.cuda.current_device()
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if wl.get("flush") else None
+    gather_out = None
+
+    def one_step():
+        out = wl["step"]()
+        if world > 1 and wl.get("gather") and out is not None:
+            nonlocal gather_out
+            if gather_out is None:
+                gather_out = torch.empty((world * out.shape[0],) + tuple(out.shape[1:]), dtype=out.dtype, device=out.device)
+            dist.all_gather_into_tensor(gather_out, out)
+
+    for _ in range(max(warmup, 3)):
+        one_step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(dev_index) if sample_clocks else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    ops.launch_count(reset=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    total_ms = 0.0
+    if flush_buf is None:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        total_ms = start.elapsed_time(end)
+    else:
+        # L2 flush between steps: time each step with its own event pair so the flush is not counted
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in evs:
+            flush_buf.fill_(1)
+            s.record()
+            one_step()
+            e.record()
+        torch.cuda.synchronize()
+        total_ms = sum(s.elapsed_time(e) for s, e in evs)
+    launches = ops.launch_count()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    ms = total_ms / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, launches, clocks
+
+
+def e2e_softmax(torch, dist, ops, steps, warmup, world):
+    """Same metric through the C ABI with HOST buffers: pinned input -> H2D -> kernel -> D2H inside the timed region."""
+    rows, cols = 8192, 4096
+    x = (3 * torch.randn(rows, cols)).pin_memory()
+    y = torch.empty(rows, cols).pin_memory()
+    shape, axes = ops._arr((rows, cols)), ops._arr((1,))
+
+    def step():
+        ops.call("docc_b200_softmax", ord("s"), 2, shape, 1, axes, x.data_ptr(), y.data_ptr(), ops.FLAG_HOST_PTRS)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    assert abs(float(y[0].sum()) - 1.0) < 1e-3  # device -> host read of the step's result
+    return {"value": world * 2 * rows * cols * 4 / (ms * 1e-3) * 1e-9, "unit": "GB/s", "ms_per_step": ms,
+            "h2d_bytes_per_step": rows * cols * 4, "d2h_bytes_per_step": rows * cols * 4,
+            "path": "docc_b200_softmax(DOCC_B200_FLAG_HOST_PTRS) on pinned host buffers, chunked H2D/kernel/D2H pipeline"}
+
+
+def cpu_softmax_baseline(budget_s=12.0, max_reps=20):
+    """Times the oracle (the reference's 7-loop-nest expansion, OpenMP on the outermost maps) on the full config."""
+    import oracle
+
+    rows, cols = 8192, 4096
+    x = (3 * np.random.RandomState(1).randn(rows, cols)).astype(np.float32)
+    oracle.softmax(x[:256], [1])
+    times = []
+    t_all = time.perf_counter()
+    while len(times) < max_reps and (time.perf_counter() - t_all) < budget_s:
+        t0 = time.perf_counter()
+        oracle.softmax(x, [1])
+        times.append(time.perf_counter() - t0)
+    best = float(np.median(times))
+    return {"value": 2 * rows * cols * 4 / best * 1e-9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"full [8192,4096] fp32 tensor, median of {len(times)} runs ({best * 1e3:.1f} ms each)",
+            "ms_per_step": best * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base = cpu_softmax_baseline(budget_s=20.0, max_reps=max(args.steps + args.warmup, 3))
+    line = {"impl": "reference", "metric": "softmax_hbm_gbs", "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "softmax fp32 [8192,4096] axis=-1 (BASELINE config 2)"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of docc's SoftmaxNode expansion (7 loop nests, 6 temporaries), OpenMP on the outermost "
+                    "map as docc's openmp target schedules it; the reference itself cannot be built without clang/MLIR/symengine"}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="softmax")
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--extra-steps", type=int, default=10)
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from docc_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ops.init(local_rank)
+    ops.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    wl = make_workload(args.workload, torch, ops, rank, world)
+    ms, launches, clocks = time_workload(wl, torch, dist, ops, args.steps, args.warmup, world, rank, sample_clocks=True)
+    peaks = measured_peaks()
+    per_gpu = wl["units"] / (ms * 1e-3) * wl["scale"]
+    value = per_gpu * (1 if wl.get("replicas_only") else world)
+    roof = {"bound": wl["bound"], "achieved": per_gpu, "peak": wl["peak"], "unit": wl["unit"],
+            "frac": (per_gpu / wl["peak"]) if wl["peak"] else None, "traffic": None,
+            "peak_source": f"of {peaks['source']}"}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as fh:
+            roof["traffic"] = json.load(fh).get(args.workload)
+
+    line = {"metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "replicas" if wl.get("replicas_only") else "weak", "vs_baseline": None, "dtype": wl["dtype"],
+            "data": "synthetic", "config": wl["config"], "roofline": roof, "gpu_launches": int(launches), "clocks": clocks}
+
+    if args.workload == "softmax":
+        line["e2e"] = e2e_softmax(torch, dist, ops, max(args.steps // 5, 5), args.warmup, world)
+        if rank == 0 and world == 1:
+            line["cpu_baseline"] = {k: v for k, v in cpu_softmax_baseline().items() if k != "ms_per_step"}
+
+    if not args.no_extras and args.workload == "softmax":
+        extras = []
+        names = ["gemm_f64", "conv_f32", "conv_bf16", "attention", "attention_causal", "block_f32", "block_bf16"]
+        for nm in names:
+            try:
+                w2 = make_workload(nm, torch, ops, rank, world)
+                if w2.get("replicas_only") and world > 1 and rank != 0:
+                    pass
+                ms2, l2, _ = time_workload(w2, torch, dist, ops, args.extra_steps, 3, world, rank)
+                pg = w2["units"] / (ms2 * 1e-3) * w2["scale"]
+                extras.append({"metric": w2["metric"], "value": pg * (1 if w2.get("replicas_only") else world),
+                               "unit": w2["unit"], "ms_per_step": ms2, "dtype": w2["dtype"], "config": w2["config"],
+                               "roofline": {"bound": w2["bound"], "achieved": pg, "peak": w2["peak"],
+                                            "frac": (pg / w2["peak"]) if w2["peak"] else None},
+                               "gpu_launches": int(l2)})
+                del w2
+                torch.cuda.empty_cache()
+            except Exception as exc:  # an extra must never take the headline line down
+                extras.append({"metric": nm, "error": f"{type(exc).__name__}: {exc}"[:300]})
+        line["extras"] = extras
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,20 @@
+// Interface between the attention entry point (attention.cu) and the tcgen05 flash kernel
+// (attention_tc.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace docc_b200 {
+
+struct AttnProblem {
+    int prec;  // 'b' or 'h'
+    int64_t B, H, Sq, Skv, D;
+    float scale;
+    int causal;
+    int64_t qs[3], ks[3], vs[3], os[3];  // element strides: batch, head, sequence (D is contiguous)
+};
+
+// Returns DOCC_B200_ERR_UNSUPPORTED for shapes the tensor-core kernel does not tile.
+int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O);
+
+}  // namespace docc_b200

@@ -1,0 +1,557 @@
+// tcgen05 contraction engine: D = epilogue(sum_p A_p * B_p) with 16-bit operands and fp32
+// accumulation in tensor memory.
+//
+// Replaces the cublas{S,D}gemm call sequence of docc's CUDA target
+// (opt/src/targets/cuda/blas/gemm.cpp:131-185) for everything except fp64.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128x64 A tiles and BNx64 B tiles into a
+//               ring of 128-byte-swizzled shared-memory stages, completion on mbarriers.
+//   warp 1      UMMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=16) four times per stage;
+//               tcgen05.commit releases the stage and, after the last k-block, publishes the
+//               accumulator. It also owns the tensor-memory allocation.
+//   warps 2-5   epilogue: tcgen05.ld the 128xBN fp32 accumulator (each warp its own 32-lane
+//               quadrant), apply alpha/beta/bias/activation/residual, store.
+// Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
+// of tile i+1. fp32 operands are handled as split bf16 (hi + lo): the kernel runs up to three
+// passes (hi*hi, hi*lo, lo*hi) into the same accumulator, which keeps fp32-level accuracy
+// (~2^-16 relative per product) at a third of the bf16 rate. Every wait is bounded.
+#include <mutex>
+
+#include "device_math.cuh"
+#include "gemm_tc.h"
+#include "ptx.cuh"
+
+namespace docc_b200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr uint32_t kABytes = kBM * kBK * 2;
+constexpr int kMaxStages = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kSmemBudget = 227 * 1024;
+
+struct TcKernelParams {
+    int M, N, K, batch;
+    int npass;
+    int pa[3], pb[3];
+    int bn;
+    int a_kmajor, b_kmajor;
+    int a_bcast, b_bcast;  // operand shared by all batch items
+    int tiles_m, tiles_n;
+    int num_kb;
+    int stages;
+    uint32_t b_bytes;
+    uint32_t idesc;
+    float alpha, beta;
+    const float* bias;
+    int bias_mode;
+    int act;
+    const void* residual;
+    long long ldr, res_bs;
+    void* out;
+    long long ldo, out_bs;
+    int out_prec;
+    int vec_out, vec_res;
+    DeviceStatus* status;
+};
+
+__device__ __forceinline__ void report_timeout(DeviceStatus* st, unsigned where) {
+    if (atomicExch(&st->timeout_flag, 1u) == 0u) st->timeout_where = where;
+    __threadfence_system();
+}
+
+template <typename OutT>
+__device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const uint32_t (&r)[16], long long row, int col0, int b) {
+    const int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
+    if (ncols <= 0) return;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
+    OutT* orow = static_cast<OutT*>(p.out) + b * p.out_bs + row * p.ldo + col0;
+    constexpr int EPV = 16 / sizeof(OutT);  // elements per 16-byte vector
+    const bool full = ncols == 16;
+    if (p.beta != 0.f) {
+        if (full && p.vec_out) {
+#pragma unroll
+            for (int q = 0; q < 16 / EPV; q++) {
+                const Pack<OutT, EPV> c = *reinterpret_cast<const Pack<OutT, EPV>*>(orow + q * EPV);
+#pragma unroll
+                for (int e = 0; e < EPV; e++) v[q * EPV + e] += p.beta * to_float(c.v[e]);
+            }
+        } else {
+            for (int j = 0; j < ncols; j++) v[j] += p.beta * to_float(orow[j]);
+        }
+    }
+    if (p.bias_mode == 1) {
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+            if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
+    } else if (p.bias_mode == 2) {
+        const float bv = __ldg(p.bias + row);
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] += bv;
+    }
+    if (p.act != DOCC_B200_ACT_NONE) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = apply_act(p.act, v[j]);
+    }
+    if (p.residual) {
+        const OutT* rrow = static_cast<const OutT*>(p.residual) + b * p.res_bs + row * p.ldr + col0;
+        if (full && p.vec_res) {
+#pragma unroll
+            for (int q = 0; q < 16 / EPV; q++) {
+                const Pack<OutT, EPV> c = *reinterpret_cast<const Pack<OutT, EPV>*>(rrow + q * EPV);
+#pragma unroll
+                for (int e = 0; e < EPV; e++) v[q * EPV + e] += to_float(c.v[e]);
+            }
+        } else {
+            for (int j = 0; j < ncols; j++) v[j] += to_float(rrow[j]);
+        }
+    }
+    if (full && p.vec_out) {
+#pragma unroll
+        for (int q = 0; q < 16 / EPV; q++) {
+            Pack<OutT, EPV> o;
+#pragma unroll
+            for (int e = 0; e < EPV; e++) o.v[e] = from_float<OutT>(v[q * EPV + e]);
+            *reinterpret_cast<Pack<OutT, EPV>*>(orow + q * EPV) = o;
+        }
+    } else {
+        for (int j = 0; j < ncols; j++) orow[j] = from_float<OutT>(v[j]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                   const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                   const TcKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sA = base;
+    const uint32_t sB = sA + uint32_t(p.stages) * kABytes;
+    const uint32_t bars = sB + uint32_t(p.stages) * p.b_bytes;
+    auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
+    auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
+    auto tfull_bar = [&](int i) { return bars + 128u + 8u * uint32_t(i); };
+    auto tempty_bar = [&](int i) { return bars + 144u + 8u * uint32_t(i); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 160u - raw_addr));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < p.stages; i++) {
+            mbar_init(full_bar(i), 1);
+            mbar_init(empty_bar(i), 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(tfull_bar(i), 1);
+            mbar_init(tempty_bar(i), 4);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmA0);
+        prefetch_tensormap(&tmB0);
+        if (p.npass > 1) {
+            prefetch_tensormap(&tmA1);
+            prefetch_tensormap(&tmB1);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    const int total_tiles = tiles_per_batch * p.batch;
+    const uint32_t stage_tx = kABytes + uint32_t(p.bn) * 128u;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int b = t / tiles_per_batch;
+                const int rem = t - b * tiles_per_batch;
+                const int n0 = (rem / p.tiles_m) * p.bn;
+                const int m0 = (rem % p.tiles_m) * kBM;
+                const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    const CUtensorMap* ma = p.pa[pass] ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = p.pb[pass] ? &tmB1 : &tmB0;
+                    for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                        const int s = int(it % uint32_t(p.stages));
+                        const uint32_t ph = (it / uint32_t(p.stages)) & 1u;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+                            report_timeout(p.status, 1);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                        const uint32_t a_dst = sA + uint32_t(s) * kABytes;
+                        const uint32_t b_dst = sB + uint32_t(s) * p.b_bytes;
+                        const int k0 = kb * kBK;
+                        if (p.a_kmajor) {
+                            tma_load_3d(a_dst, ma, full_bar(s), k0, m0, ba);
+                        } else {
+                            tma_load_3d(a_dst, ma, full_bar(s), m0, k0, ba);
+                            tma_load_3d(a_dst + 8192u, ma, full_bar(s), m0 + 64, k0, ba);
+                        }
+                        if (p.b_kmajor) {
+                            tma_load_3d(b_dst, mb, full_bar(s), k0, n0, bb);
+                        } else {
+                            for (int j = 0; j < p.bn / 64; j++)
+                                tma_load_3d(b_dst + uint32_t(j) * 8192u, mb, full_bar(s), n0 + 64 * j, k0, bb);
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                // let copies already in flight land before the CTA retires
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            uint32_t lt = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
+                const uint32_t buf = lt & 1u;
+                const uint32_t use = lt >> 1;
+                if (!mbar_wait(tempty_bar(int(buf)), (use & 1u) ^ 1u)) {
+                    report_timeout(p.status, 2);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                        const int s = int(it % uint32_t(p.stages));
+                        const uint32_t ph = (it / uint32_t(p.stages)) & 1u;
+                        if (!mbar_wait(full_bar(s), ph)) {
+                            report_timeout(p.status, 3);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t a_base = sA + uint32_t(s) * kABytes;
+                        const uint32_t b_base = sB + uint32_t(s) * p.b_bytes;
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; kk++) {
+                            const uint64_t da = p.a_kmajor ? make_smem_desc(a_base + uint32_t(kk) * 32u, 16u, 1024u)
+                                                           : make_smem_desc(a_base + uint32_t(kk) * 2048u, 8192u, 1024u);
+                            const uint64_t db = p.b_kmajor ? make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u)
+                                                           : make_smem_desc(b_base + uint32_t(kk) * 2048u, 8192u, 1024u);
+                            umma_f16_ss(d_tmem, da, db, p.idesc, acc);
+                            acc = 1;
+                        }
+                        umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(int(buf)));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+        uint32_t lt = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
+            const uint32_t buf = lt & 1u;
+            const uint32_t use = lt >> 1;
+            const int b = t / tiles_per_batch;
+            const int rem = t - b * tiles_per_batch;
+            const int n0 = (rem / p.tiles_m) * p.bn;
+            const int m0 = (rem % p.tiles_m) * kBM;
+            if (!mbar_wait(tfull_bar(int(buf)), use & 1u)) {
+                if (lane == 0) report_timeout(p.status, 4);
+                break;
+            }
+            tc_fence_after();
+            const long long row = m0 + q * 32 + lane;
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
+            for (int c = 0; c < p.bn; c += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(t_addr + uint32_t(c), r);
+                tmem_ld_wait();
+                if (row < p.M) {
+                    if (p.out_prec == DOCC_B200_PREC_S) epilogue_chunk<float>(p, r, row, n0 + c, b);
+                    else if (p.out_prec == DOCC_B200_PREC_B) epilogue_chunk<__nv_bfloat16>(p, r, row, n0 + c, b);
+                    else epilogue_chunk<__half>(p, r, row, n0 + c, b);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(int(buf)));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- fp32 -> bf16 hi/lo split ---------------------------------------------------------------------
+__device__ __forceinline__ void split1(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ X, int64_t rows, int64_t cols, int64_t ld,
+                                                         int64_t bs, __nv_bfloat16* __restrict__ hi,
+                                                         __nv_bfloat16* __restrict__ lo, int64_t ldo, int64_t obs, int vec) {
+    const int64_t b = blockIdx.z;
+    X += b * bs;
+    hi += b * obs;
+    lo += b * obs;
+    if (vec) {
+        const int64_t cpr = cols / 4;
+        const int64_t total = rows * cpr;
+        for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+            const int64_t r = i / cpr, c = (i - r * cpr) * 4;
+            const float4 x = *reinterpret_cast<const float4*>(X + r * ld + c);
+            Pack<__nv_bfloat16, 4> h, l;
+            split1(x.x, h.v[0], l.v[0]);
+            split1(x.y, h.v[1], l.v[1]);
+            split1(x.z, h.v[2], l.v[2]);
+            split1(x.w, h.v[3], l.v[3]);
+            *reinterpret_cast<Pack<__nv_bfloat16, 4>*>(hi + r * ldo + c) = h;
+            *reinterpret_cast<Pack<__nv_bfloat16, 4>*>(lo + r * ldo + c) = l;
+        }
+    } else {
+        const int64_t total = rows * cols;
+        for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+            const int64_t r = i / cols, c = i - r * cols;
+            split1(X[r * ld + c], hi[r * ldo + c], lo[r * ldo + c]);
+        }
+    }
+}
+
+// out[c][r] = split(X[r][c]); 32x32 tiles through shared memory keep both sides coalesced.
+__global__ void __launch_bounds__(256) split_transpose_kernel(const float* __restrict__ X, int64_t rows, int64_t cols,
+                                                              int64_t ld, int64_t bs, __nv_bfloat16* __restrict__ hi,
+                                                              __nv_bfloat16* __restrict__ lo, int64_t ldo, int64_t obs) {
+    __shared__ float tile[32][33];
+    const int64_t b = blockIdx.z;
+    X += b * bs;
+    hi += b * obs;
+    lo += b * obs;
+    const int64_t tiles_c = (cols + 31) / 32, tiles_r = (rows + 31) / 32;
+    for (int64_t t = blockIdx.x; t < tiles_c * tiles_r; t += gridDim.x) {
+        const int64_t r0 = (t / tiles_c) * 32, c0 = (t % tiles_c) * 32;
+        const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+        for (int j = ty; j < 32; j += 8) {
+            const int64_t r = r0 + j, c = c0 + tx;
+            tile[j][tx] = (r < rows && c < cols) ? X[r * ld + c] : 0.f;
+        }
+        __syncthreads();
+        for (int j = ty; j < 32; j += 8) {
+            const int64_t c = c0 + j, r = r0 + tx;
+            if (c < cols && r < rows) split1(tile[tx][j], hi[c * ldo + r], lo[c * ldo + r]);
+        }
+        __syncthreads();
+    }
+}
+
+// ---- tensor map encoding --------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+int get_encode(EncodeFn* fn) {
+    std::call_once(g_encode_once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeFn>(f);
+        else
+            (void)cudaGetLastError();
+    });
+    if (!g_encode) return set_error(DOCC_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    *fn = g_encode;
+    return DOCC_B200_OK;
+}
+
+bool g_attr_set[16] = {false};
+
+}  // namespace
+
+int encode_tmap(CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_size, CUtensorMapSwizzle swizzle, const void* base,
+                int rank, const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+    EncodeFn fn;
+    DOCC_TRY(get_encode(&fn));
+    cuuint64_t gd[5], gs[5];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; i++) {
+        gd[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i > 0) gs[i - 1] = strides_bytes[i - 1];
+    }
+    (void)elem_size;
+    CUresult r = fn(map, dtype, cuuint32_t(rank), const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return set_error(DOCC_B200_ERR_CUDA,
+                         "cuTensorMapEncodeTiled failed (%d): rank %d dims [%llu,%llu,%llu,%llu] strides [%llu,%llu,%llu] box "
+                         "[%u,%u,%u,%u] base %p",
+                         int(r), rank, (unsigned long long)gd[0], (unsigned long long)(rank > 1 ? gd[1] : 0),
+                         (unsigned long long)(rank > 2 ? gd[2] : 0), (unsigned long long)(rank > 3 ? gd[3] : 0),
+                         (unsigned long long)(rank > 1 ? gs[0] : 0), (unsigned long long)(rank > 2 ? gs[1] : 0),
+                         (unsigned long long)(rank > 3 ? gs[2] : 0), bx[0], rank > 1 ? bx[1] : 0, rank > 2 ? bx[2] : 0,
+                         rank > 3 ? bx[3] : 0, base);
+    }
+    return DOCC_B200_OK;
+}
+
+int encode_tmap_16bit(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                      const uint32_t* box) {
+    return encode_tmap(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_128B, base, rank, dims, strides_bytes, box);
+}
+
+int split_f32_to_bf16x2(Ctx* ctx, const float* X, int64_t rows, int64_t cols, int64_t ld, int64_t batch, int64_t batch_stride,
+                        bool transpose, __nv_bfloat16* hi, __nv_bfloat16* lo, int64_t ld_out, int64_t out_batch_stride) {
+    if (rows == 0 || cols == 0 || batch == 0) return DOCC_B200_OK;
+    const int64_t cap = int64_t(ctx->sm_count) * 8;
+    if (!transpose) {
+        const int vec = (cols % 4 == 0 && ld % 4 == 0 && ld_out % 4 == 0 && batch_stride % 4 == 0 && out_batch_stride % 4 == 0 &&
+                         reinterpret_cast<uintptr_t>(X) % 16 == 0 && reinterpret_cast<uintptr_t>(hi) % 8 == 0 &&
+                         reinterpret_cast<uintptr_t>(lo) % 8 == 0)
+                            ? 1
+                            : 0;
+        const int64_t items = vec ? rows * cols / 4 : rows * cols;
+        int64_t blocks = ceil_div(items, 256);
+        if (blocks > cap) blocks = cap;
+        dim3 grid(unsigned(blocks), 1, unsigned(batch));
+        split_rows_kernel<<<grid, 256, 0, ctx->stream>>>(X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride, vec);
+        return after_launch(ctx, "split_rows_kernel");
+    }
+    int64_t blocks = ceil_div(rows, 32) * ceil_div(cols, 32);
+    if (blocks > cap) blocks = cap;
+    dim3 grid(unsigned(blocks), 1, unsigned(batch));
+    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride);
+    return after_launch(ctx, "split_transpose_kernel");
+}
+
+int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t batch, int npass, const TcOperand* A, const int* pa,
+            const TcOperand* B, const int* pb, const TcEpilogue& ep) {
+    if (M == 0 || N == 0 || batch == 0) return DOCC_B200_OK;
+    if (K <= 0) return set_error(DOCC_B200_ERR_UNSUPPORTED, "tc_gemm: K must be positive");
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535 * 64) return set_error(DOCC_B200_ERR_UNSUPPORTED, "tc_gemm: extent too large");
+    if (npass < 1 || npass > 3) return set_error(DOCC_B200_ERR_INVALID_ARG, "tc_gemm: npass %d", npass);
+    int n_a = 0, n_b = 0;
+    for (int i = 0; i < npass; i++) {
+        if (pa[i] + 1 > n_a) n_a = pa[i] + 1;
+        if (pb[i] + 1 > n_b) n_b = pb[i] + 1;
+    }
+    auto aligned = [](const TcOperand& o) {
+        return reinterpret_cast<uintptr_t>(o.ptr) % 16 == 0 && o.ld % 8 == 0 && o.batch_stride % 8 == 0;
+    };
+    for (int i = 0; i < n_a; i++)
+        if (!aligned(A[i]) || A[i].k_major != A[0].k_major) return set_error(DOCC_B200_ERR_UNSUPPORTED, "tc_gemm: A operand not 16-byte aligned");
+    for (int i = 0; i < n_b; i++)
+        if (!aligned(B[i]) || B[i].k_major != B[0].k_major) return set_error(DOCC_B200_ERR_UNSUPPORTED, "tc_gemm: B operand not 16-byte aligned");
+
+    TcKernelParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = int(M); p.N = int(N); p.K = int(K); p.batch = int(batch);
+    p.npass = npass;
+    for (int i = 0; i < npass; i++) { p.pa[i] = pa[i]; p.pb[i] = pb[i]; }
+    p.a_kmajor = A[0].k_major ? 1 : 0;
+    p.b_kmajor = B[0].k_major ? 1 : 0;
+    p.a_bcast = (batch > 1 && A[0].batch_stride == 0) ? 1 : 0;
+    p.b_bcast = (batch > 1 && B[0].batch_stride == 0) ? 1 : 0;
+
+    // N tile: the largest of 256/128/64 that still yields at least one tile per SM; MN-major B
+    // needs multiples of 64, small N uses the next multiple of 16.
+    const int64_t tiles_m = ceil_div(M, kBM);
+    int bn;
+    if (N <= 64) {
+        bn = p.b_kmajor ? int(ceil_div(N, 16) * 16) : 64;
+    } else {
+        bn = 256;
+        while (bn > 64 && (bn / 2 >= N || tiles_m * ceil_div(N, bn) * batch < ctx->sm_count)) bn /= 2;
+        if (bn > 64 && N <= bn / 2) bn /= 2;
+    }
+    p.bn = bn;
+    p.tiles_m = int(tiles_m);
+    p.tiles_n = int(ceil_div(N, bn));
+    p.num_kb = int(ceil_div(K, kBK));
+    p.b_bytes = uint32_t((bn * 128 + 1023) / 1024 * 1024);
+    int stages = (kSmemBudget - 2048) / int(kABytes + p.b_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    const int64_t k_iters = int64_t(p.num_kb) * npass;
+    if (stages > k_iters && k_iters >= 2) stages = int(k_iters);
+    if (stages < 2) stages = 2;
+    p.stages = stages;
+    p.idesc = make_idesc(kBM, bn, ab_format, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+
+    p.alpha = ep.alpha; p.beta = ep.beta;
+    p.bias = ep.bias; p.bias_mode = ep.bias ? ep.bias_mode : 0;
+    p.act = ep.act;
+    p.residual = ep.residual; p.ldr = ep.ldr; p.res_bs = ep.residual_batch_stride;
+    p.out = ep.out; p.ldo = ep.ldo; p.out_bs = ep.out_batch_stride; p.out_prec = ep.out_prec;
+    const size_t oes = prec_size(ep.out_prec);
+    if (oes != 2 && oes != 4) return set_error(DOCC_B200_ERR_INVALID_ARG, "tc_gemm: output precision %d", ep.out_prec);
+    const int64_t epv = 16 / int64_t(oes);
+    p.vec_out = (reinterpret_cast<uintptr_t>(ep.out) % 16 == 0 && ep.ldo % epv == 0 && ep.out_batch_stride % epv == 0) ? 1 : 0;
+    p.vec_res = (ep.residual && reinterpret_cast<uintptr_t>(ep.residual) % 16 == 0 && ep.ldr % epv == 0 &&
+                 ep.residual_batch_stride % epv == 0)
+                    ? 1
+                    : 0;
+    p.status = ctx->status_dev;
+
+    CUtensorMap maps[4];
+    memset(maps, 0, sizeof(maps));
+    auto encode_operand = [&](CUtensorMap* m, const TcOperand& o, int64_t mn, uint32_t mn_box, bool bcast) -> int {
+        const uint64_t nb = bcast ? 1 : uint64_t(batch);
+        uint64_t bs_bytes = uint64_t(o.batch_stride) * 2;
+        if (nb == 1 || bs_bytes == 0) bs_bytes = uint64_t(o.ld) * 2 * uint64_t(o.k_major ? mn : K);
+        if (o.k_major) {
+            const uint64_t dims[3] = {uint64_t(K), uint64_t(mn), nb};
+            const uint64_t strides[2] = {uint64_t(o.ld) * 2, bs_bytes};
+            const uint32_t box[3] = {uint32_t(kBK), mn_box, 1};
+            return encode_tmap_16bit(m, o.ptr, 3, dims, strides, box);
+        }
+        const uint64_t dims[3] = {uint64_t(mn), uint64_t(K), nb};
+        const uint64_t strides[2] = {uint64_t(o.ld) * 2, bs_bytes};
+        const uint32_t box[3] = {64, uint32_t(kBK), 1};
+        return encode_tmap_16bit(m, o.ptr, 3, dims, strides, box);
+    };
+    for (int i = 0; i < 2; i++) {
+        DOCC_TRY(encode_operand(&maps[i], A[i < n_a ? i : 0], M, kBM, p.a_bcast || batch == 1));
+        DOCC_TRY(encode_operand(&maps[2 + i], B[i < n_b ? i : 0], N, uint32_t(bn), p.b_bcast || batch == 1));
+    }
+
+    const size_t smem = size_t(stages) * (kABytes + p.b_bytes) + 1024 + 256;
+    if (!g_attr_set[ctx->device & 15]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+        g_attr_set[ctx->device & 15] = true;
+    }
+    const int64_t total_tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
+    const int grid = int(total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count);
+    tc_gemm_kernel<<<grid, kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    return after_launch(ctx, "tc_gemm_kernel");
+}
+
+}  // namespace docc_b200
