@@ -1,10 +1,402 @@
-// Flash attention on the tcgen05 engine.
+// Flash attention on tcgen05: O = softmax(scale * Q K^T [+ causal mask]) V for 16-bit inputs,
+// head_dim 64 or 128, fp32 accumulation. The Sq x Skv score matrix never leaves the SM.
+//
+// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key/value sequence
+// in blocks of 128. 192 threads:
+//   warp 0     TMA producer: Q once, then K_j / V_j into two-deep rings.
+//   warp 1     UMMA issuer:  S_j = Q K_j^T  (M=128, N=128, K=D) into one of two TMEM score buffers,
+//                            O_j = P_j V_j  (M=128, N=D,  K=128) into one of two TMEM output buffers.
+//   warps 2-5  softmax: thread r owns query row r. Per block: tcgen05.ld the row of S_j, running
+//              max / sum in the exp2 domain, P_j (16-bit) written to shared memory in the 128-byte
+//              swizzled K-major layout UMMA reads, then (one block later, so the tensor pipe never
+//              waits on it) acc = acc * corr_j + O_j from TMEM into registers.
+// QK^T of block j+1 is issued before P_j V_j, so the tensor pipe computes the next scores while the
+// softmax warps work on the current ones. All waits are bounded.
 #include "attention.h"
+#include "device_math.cuh"
+#include "gemm_tc.h"
+#include "ptx.cuh"
 
 namespace docc_b200 {
+namespace {
 
-int attention_tc(Ctx*, const AttnProblem&, const void*, const void*, const void*, void*) {
-    return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: not available");
+using namespace ptx;
+
+constexpr int kBQ = 128;   // query rows per CTA
+constexpr int kBKV = 128;  // keys per block
+constexpr int kAttnThreads = 192;
+
+struct AttnKernelParams {
+    int Sq, Skv, H;
+    int n_qtiles;
+    int causal;
+    int causal_off;  // Skv - Sq: query i sees keys j <= i + causal_off
+    float scale_log2;  // scale * log2(e)
+    void* O;
+    long long os_b, os_h, os_s;
+    DeviceStatus* status;
+};
+
+__device__ __forceinline__ void attn_timeout(DeviceStatus* st, unsigned where) {
+    volatile unsigned int* f = &st->timeout_flag;
+    volatile unsigned int* w = &st->timeout_where;
+    if (*w == 0u) *w = where;
+    *f = 1u;
+    __threadfence_system();
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+template <bool IS_BF16> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if constexpr (IS_BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
+// Shared memory map (offsets from a 1024-byte aligned base):
+//   Q   : D/64 chunks of [128 rows][128 B]            = 16 KB * D/64
+//   K[2]: same shape per stage
+//   V[2]: D/64 chunks of [128 kv rows][128 B] per stage (MN-major for the P V product)
+//   P   : 2 chunks of [128 rows][128 B]                = 32 KB
+template <int D, bool IS_BF16>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+    attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const AttnKernelParams p) {
+    constexpr int DC = D / 64;                      // 64-element chunks along head_dim
+    constexpr uint32_t kTile = uint32_t(DC) * 16384u;  // bytes of one Q / K / V tile
+    constexpr uint32_t kPBytes = 32768u;
+    constexpr uint32_t kTmemCols = 512;
+    constexpr uint32_t kSCol = 0;      // two score buffers of 128 columns
+    constexpr uint32_t kOCol = 256;    // two output buffers, 128 columns apart
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sQ = base;
+    const uint32_t sK = sQ + kTile;
+    const uint32_t sV = sK + 2 * kTile;
+    const uint32_t sP = sV + 2 * kTile;
+    const uint32_t bars = sP + kPBytes;
+    const uint32_t q_full = bars;
+    auto k_full = [&](int i) { return bars + 8u + 8u * uint32_t(i); };
+    auto k_empty = [&](int i) { return bars + 24u + 8u * uint32_t(i); };
+    auto v_full = [&](int i) { return bars + 40u + 8u * uint32_t(i); };
+    auto v_empty = [&](int i) { return bars + 56u + 8u * uint32_t(i); };
+    auto s_full = [&](int i) { return bars + 72u + 8u * uint32_t(i); };
+    auto s_empty = [&](int i) { return bars + 88u + 8u * uint32_t(i); };
+    auto o_full = [&](int i) { return bars + 104u + 8u * uint32_t(i); };
+    const uint32_t p_full = bars + 120u;
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 128u - raw_addr));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // heavier (later) query tiles first under a causal mask
+    const int qt_raw = blockIdx.x % p.n_qtiles;
+    const int qtile = p.causal ? p.n_qtiles - 1 - qt_raw : qt_raw;
+    const int bh = blockIdx.x / p.n_qtiles;
+    const int h = bh % p.H, b = bh / p.H;
+    const int q0 = qtile * kBQ;
+    // keys this tile can see
+    int kv_end = p.Skv;
+    if (p.causal) {
+        const int last = q0 + kBQ - 1 + p.causal_off;  // last key visible to the last row of the tile
+        kv_end = last + 1 < p.Skv ? last + 1 : p.Skv;
+        if (kv_end < 0) kv_end = 0;
+    }
+    const int n_blocks = (kv_end + kBKV - 1) / kBKV;
+
+    if (warp == 0 && lane == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(k_full(i), 1);
+            mbar_init(k_empty(i), 1);
+            mbar_init(v_full(i), 1);
+            mbar_init(v_empty(i), 1);
+            mbar_init(s_full(i), 1);
+            mbar_init(s_empty(i), 4);
+            mbar_init(o_full(i), 1);
+        }
+        mbar_init(p_full, 4);
+        fence_barrier_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && n_blocks > 0) {
+            mbar_arrive_expect_tx(q_full, kTile);
+            for (int c = 0; c < DC; c++) tma_load_4d(sQ + uint32_t(c) * 16384u, &tmQ, q_full, c * 64, q0, h, b);
+            for (int j = 0; j < n_blocks; j++) {
+                const int s = j & 1;
+                const uint32_t ph = uint32_t(j >> 1) & 1u;
+                if (!mbar_wait(k_empty(s), ph ^ 1u)) { attn_timeout(p.status, 11); break; }
+                mbar_arrive_expect_tx(k_full(s), kTile);
+                for (int c = 0; c < DC; c++)
+                    tma_load_4d(sK + uint32_t(s) * kTile + uint32_t(c) * 16384u, &tmK, k_full(s), c * 64, j * kBKV, h, b);
+                if (!mbar_wait(v_empty(s), ph ^ 1u)) { attn_timeout(p.status, 12); break; }
+                mbar_arrive_expect_tx(v_full(s), kTile);
+                for (int c = 0; c < DC; c++)
+                    tma_load_4d(sV + uint32_t(s) * kTile + uint32_t(c) * 16384u, &tmV, v_full(s), c * 64, j * kBKV, h, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0 && n_blocks > 0) {
+            constexpr uint32_t idesc_qk = make_idesc(kBQ, kBKV, IS_BF16 ? 1 : 0, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc(kBQ, D, IS_BF16 ? 1 : 0, 0, 1);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) attn_timeout(p.status, 13);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                const uint32_t ph = uint32_t(j >> 1) & 1u;
+                if (!mbar_wait(k_full(s), ph)) { attn_timeout(p.status, 14); return false; }
+                if (!mbar_wait(s_empty(s), ph ^ 1u)) { attn_timeout(p.status, 15); return false; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + kSCol + uint32_t(s) * 128u;
+                const uint32_t kb = sK + uint32_t(s) * kTile;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t off = uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u;
+                    umma_f16_ss(d_tmem, make_smem_desc(sQ + off, 16u, 1024u), make_smem_desc(kb + off, 16u, 1024u), idesc_qk,
+                                kk > 0 ? 1u : 0u);
+                }
+                umma_commit(k_empty(s));
+                umma_commit(s_full(s));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_blocks && ok; j++) {
+                if (j + 1 < n_blocks) {
+                    ok = issue_qk(j + 1);
+                    if (!ok) break;
+                }
+                const int s = j & 1;
+                const uint32_t ph = uint32_t(j >> 1) & 1u;
+                if (!mbar_wait(v_full(s), ph)) { attn_timeout(p.status, 16); break; }
+                if (!mbar_wait(p_full, uint32_t(j) & 1u)) { attn_timeout(p.status, 17); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + kOCol + uint32_t(s) * 128u;
+                const uint32_t vb = sV + uint32_t(s) * kTile;
+#pragma unroll
+                for (int kk = 0; kk < kBKV / 16; kk++) {
+                    // P: K-major, two 64-key chunks of 16 KB. V: MN-major, D/64 chunks of 16 KB, 16 key rows = 2 KB.
+                    const uint64_t da = make_smem_desc(sP + uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u, 16u, 1024u);
+                    const uint64_t db = make_smem_desc(vb + uint32_t(kk) * 2048u, 16384u, 1024u);
+                    umma_f16_ss(d_tmem, da, db, idesc_pv, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(v_empty(s));
+                umma_commit(o_full(s));
+            }
+        }
+    } else {
+        // ---------------- softmax / accumulate / store ----------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;  // row inside the tile == TMEM lane
+        const int row = q0 + r;
+        const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
+        float acc[D];
+#pragma unroll
+        for (int i = 0; i < D; i++) acc[i] = 0.f;
+        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        bool ok = true;
+        const int row_limit = p.causal ? row + p.causal_off : p.Skv - 1;  // last visible key of this row
+
+        auto accumulate = [&](int j, float corr) -> bool {
+            const int s = j & 1;
+            if (!mbar_wait(o_full(s), uint32_t(j >> 1) & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 18);
+                return false;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t o[32];
+                tmem_ld_x32(lane_addr + kOCol + uint32_t(s) * 128u + uint32_t(c) * 32u, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++) acc[c * 32 + i] = fmaf(acc[c * 32 + i], corr, __uint_as_float(o[i]));
+            }
+            return true;
+        };
+
+        for (int j = 0; j < n_blocks && ok; j++) {
+            const int s = j & 1;
+            const int k0 = j * kBKV;
+            if (!mbar_wait(s_full(s), uint32_t(j >> 1) & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 19);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + kSCol + uint32_t(s) * 128u;
+            const bool need_mask = (k0 + kBKV > p.Skv) || (p.causal && k0 + kBKV - 1 > q0 + p.causal_off);
+            const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;  // local index of the last visible key
+            // pass 1: block maximum
+            float bm = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kBKV / 32; c++) {
+                uint32_t sv[32];
+                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i <= visible) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                }
+            }
+            const float m_new = fmaxf(m, bm * p.scale_log2);
+            const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+            const float corr = ex2(m - m_ref);  // 0 on the first block (m = -inf)
+            // P_{j-1} must have been consumed by the tensor pipe before P_j overwrites it
+            if (j > 0) {
+                if (!mbar_wait(o_full((j - 1) & 1), uint32_t((j - 1) >> 1) & 1u)) {
+                    if (lane == 0) attn_timeout(p.status, 20);
+                    ok = false;
+                    break;
+                }
+            }
+            // pass 2: exponentials, row sum, P to shared memory
+            float bl = 0.f;
+#pragma unroll
+            for (int c = 0; c < kBKV / 32; c++) {
+                uint32_t sv[32];
+                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
+                tmem_ld_wait();
+                float e[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float x = ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -m_ref));
+                    if (need_mask && c * 32 + i > visible) x = 0.f;
+                    e[i] = x;
+                    bl += x;
+                }
+                // 32 keys = four 16-byte units; unit u of the row lands at (u ^ (r & 7)) in its 128-byte line
+#pragma unroll
+                for (int u4 = 0; u4 < 4; u4++) {
+                    const int u = (c * 4 + u4) & 7;
+                    const uint32_t dst = sP + uint32_t(c / 2) * 16384u + uint32_t(r) * 128u + uint32_t((u ^ (r & 7)) * 16);
+                    const uint32_t w0 = pack2<IS_BF16>(e[u4 * 8 + 0], e[u4 * 8 + 1]);
+                    const uint32_t w1 = pack2<IS_BF16>(e[u4 * 8 + 2], e[u4 * 8 + 3]);
+                    const uint32_t w2 = pack2<IS_BF16>(e[u4 * 8 + 4], e[u4 * 8 + 5]);
+                    const uint32_t w3 = pack2<IS_BF16>(e[u4 * 8 + 6], e[u4 * 8 + 7]);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                }
+            }
+            l = l * corr + bl;
+            m = m_new;
+            // S_j is free for Q K_{j+2}^T; P_j is ready for the tensor pipe
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty(s));
+                mbar_arrive(p_full);
+            }
+            // fold in the previous block's P V while the tensor pipe works on this one
+            if (j > 0) ok = accumulate(j - 1, corr_prev);
+            corr_prev = corr;
+        }
+        if (ok && n_blocks > 0) ok = accumulate(n_blocks - 1, corr_prev);
+
+        if (row < p.Sq) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            using T = typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type;
+            T* o = static_cast<T*>(p.O) + b * p.os_b + h * p.os_h + (long long)row * p.os_s;
+#pragma unroll
+            for (int c = 0; c < D / 8; c++) {
+                uint4 w;
+                w.x = pack2<IS_BF16>(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
+                w.y = pack2<IS_BF16>(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
+                w.z = pack2<IS_BF16>(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
+                w.w = pack2<IS_BF16>(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
+                *reinterpret_cast<uint4*>(o + c * 8) = w;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+bool g_attr_done[16][4] = {};
+
+template <int D, bool IS_BF16>
+int launch(Ctx* ctx, const AttnProblem& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+           const AttnKernelParams& kp, int slot) {
+    constexpr size_t smem = size_t(D / 64) * 16384 * 5 + 32768 + 1024 + 256;
+    auto kern = attention_tc_kernel<D, IS_BF16>;
+    if (!g_attr_done[ctx->device & 15][slot]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        g_attr_done[ctx->device & 15][slot] = true;
+    }
+    const int64_t grid = p.B * p.H * kp.n_qtiles;
+    kern<<<unsigned(grid), kAttnThreads, smem, ctx->stream>>>(tq, tk, tv, kp);
+    return after_launch(ctx, "attention_tc_kernel");
+}
+
+}  // namespace
+
+int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O) {
+    if (p.D != 64 && p.D != 128) return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: head_dim %lld", (long long)p.D);
+    if (p.Skv <= 0 || p.Sq <= 0) return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: empty sequence");
+    // the block maximum is taken before scaling, which needs a positive scale
+    if (!(p.scale > 0.f)) return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: non-positive scale");
+    auto ok_strides = [](const void* ptr, const int64_t* s) {
+        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && s[0] % 8 == 0 && s[1] % 8 == 0 && s[2] % 8 == 0 && s[2] > 0;
+    };
+    if (!ok_strides(Q, p.qs) || !ok_strides(K, p.ks) || !ok_strides(V, p.vs) || !ok_strides(O, p.os))
+        return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: strides are not multiples of 16 bytes");
+    if (p.B * p.H * ceil_div(p.Sq, kBQ) > 0x7fffffff || p.Sq > INT32_MAX / 2 || p.Skv > INT32_MAX / 2)
+        return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc: extent too large");
+
+    auto encode = [&](CUtensorMap* m, const void* ptr, const int64_t* s, int64_t S) -> int {
+        // dims innermost first: D, S, H, B. A size-1 dim still needs a legal (16-byte multiple) stride.
+        const uint64_t dims[4] = {uint64_t(p.D), uint64_t(S), uint64_t(p.H), uint64_t(p.B)};
+        auto st = [&](int64_t v) { return uint64_t(v > 0 ? v : p.D) * 2; };
+        const uint64_t strides[3] = {st(s[2]), st(s[1]), st(s[0])};
+        const uint32_t box[4] = {64, 128, 1, 1};
+        return encode_tmap_16bit(m, ptr, 4, dims, strides, box);
+    };
+    CUtensorMap tq, tk, tv;
+    DOCC_TRY(encode(&tq, Q, p.qs, p.Sq));
+    DOCC_TRY(encode(&tk, K, p.ks, p.Skv));
+    DOCC_TRY(encode(&tv, V, p.vs, p.Skv));
+
+    AttnKernelParams kp;
+    kp.Sq = int(p.Sq); kp.Skv = int(p.Skv); kp.H = int(p.H);
+    kp.n_qtiles = int(ceil_div(p.Sq, kBQ));
+    kp.causal = p.causal;
+    kp.causal_off = int(p.Skv - p.Sq);
+    kp.scale_log2 = p.scale * 1.4426950408889634f;
+    kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
+    kp.status = ctx->status_dev;
+    const bool bf = p.prec == DOCC_B200_PREC_B;
+    if (p.D == 128) return bf ? launch<128, true>(ctx, p, tq, tk, tv, kp, 0) : launch<128, false>(ctx, p, tq, tk, tv, kp, 1);
+    return bf ? launch<64, true>(ctx, p, tq, tk, tv, kp, 2) : launch<64, false>(ctx, p, tq, tk, tv, kp, 3);
 }
 
 }  // namespace docc_b200

@@ -61,7 +61,11 @@ struct TcKernelParams {
 };
 
 __device__ __forceinline__ void report_timeout(DeviceStatus* st, unsigned where) {
-    if (atomicExch(&st->timeout_flag, 1u) == 0u) st->timeout_where = where;
+    // plain stores into mapped host memory (system-scope atomics over PCIe are not guaranteed)
+    volatile unsigned int* f = &st->timeout_flag;
+    volatile unsigned int* w = &st->timeout_where;
+    if (*w == 0u) *w = where;
+    *f = 1u;
     __threadfence_system();
 }
 

@@ -94,8 +94,13 @@ def sync() -> None:
 
 
 def set_stream(stream_handle) -> None:
-    """Route launches of the calling thread to ``stream_handle`` (a cudaStream_t value); None restores the library's stream."""
-    call("docc_b200_set_stream", _vp(stream_handle or 0))
+    """Route launches of the calling thread to ``stream_handle`` (a cudaStream_t value, e.g.
+    ``torch.cuda.current_stream().cuda_stream``). ``None`` restores the library's own stream; the
+    value 0 names the legacy default stream and is passed on as CUDA's ``cudaStreamLegacy`` handle."""
+    if stream_handle is None:
+        call("docc_b200_set_stream", _vp(0))
+    else:
+        call("docc_b200_set_stream", _vp(int(stream_handle) or 1))
 
 
 def launch_count(reset: bool = False) -> int:

@@ -114,7 +114,9 @@ int docc_b200_host_free(void* hptr);
 int docc_b200_set_alloc_limit(size_t bytes);
 
 /* Stream control. `stream` is a cudaStream_t; NULL restores the library's own
- * per-thread stream. Replaces the implicit default stream of generated code. */
+ * per-thread stream. CUDA's special handles cudaStreamLegacy ((cudaStream_t)0x1)
+ * and cudaStreamPerThread ((cudaStream_t)0x2) name the default streams.
+ * Replaces the implicit default stream of generated code. */
 int docc_b200_set_stream(void* stream);
 int docc_b200_get_stream(void** stream);
 /* Waits for everything queued on the calling thread's stream
