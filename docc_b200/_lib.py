@@ -48,6 +48,7 @@ SIGNATURES = {
     "docc_b200_last_error": (ctypes.c_char_p, []),
     "docc_b200_launch_count": (_i64, [_int]),
     "docc_b200_gemm": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _int]),
+    "docc_b200_gemm_f32_noalloc": (_int, [_int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64, _vp]),
     "docc_b200_matmul": (_int, [_int, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _int]),
     "docc_b200_gemm_epilogue": (_int, [_int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _vp, _int, _vp, _i64, _vp, _i64, _int]),
     "docc_b200_softmax": (_int, [_int, _int, _pi64, _int, _pi64, _vp, _vp, _int]),

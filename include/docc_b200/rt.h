@@ -141,6 +141,24 @@ int docc_b200_gemm(int prec, int layout, int transa, int transb,
                    const void* B, int64_t ldb,
                    const void* beta, void* C, int64_t ldc, int flags);
 
+/* Row-major fp32 GEMM C = alpha * op(A) * op(B) + beta * C on device pointers that allocates
+ * nothing (no counterpart in the reference; docc's cuBLAS path allocates on every call).
+ * For embedders that cannot allocate device memory once they are running: a host application
+ * that gave the whole GPU to its own allocator at start-up, or a latency-critical loop that
+ * cannot take the device-wide synchronisation of cudaMalloc / cudaFree. The bf16 hi/lo planes
+ * of A and B live in a fixed 16 MiB array inside the library image (held by every GPU that
+ * loads the library until the process exits), so 4 * (m + n) * roundup8(k) bytes must fit in
+ * 16 MiB; larger problems return DOCC_B200_ERR_INVALID_ARG. k >= 1. `stream` is the
+ * cudaStream_t to run on; the call returns once C is complete. All calls share the array
+ * (it keeps the previous call's contents), so calls that overlap on the GPU race: serialise
+ * them. The first call on a device looks up the array's device address and sets a kernel
+ * attribute; make it before any stream capture. Same kernels and pass order as
+ * docc_b200_gemm('s'), so results are identical to it. */
+int docc_b200_gemm_f32_noalloc(int transa, int transb, int64_t m, int64_t n, int64_t k,
+                               float alpha, const float* A, int64_t lda,
+                               const float* B, int64_t ldb,
+                               float beta, float* C, int64_t ldc, void* stream);
+
 /* Batched row-major matmul Y[b] = A[b] * B[b]: the loop nest MatMulNode::expand
  * wraps around GEMMNode (matmul_node.cpp:286-544; lda = strides_a[-2], ldc = N,
  * :463-489). A batch stride of 0 broadcasts that operand. */
