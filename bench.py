@@ -142,6 +142,24 @@ def make_workload(name, torch, ops, rank, world):
                     config={"workload": "GEMM fp64 1000x1000x1000 (BASELINE config 1)", "l2": "flushed between steps"},
                     flush=True, kind="gemm", replicas_only=True)
 
+    if name in ("gemm_bf16", "gemm_f32"):
+        # not a BASELINE config: the engine's own large-GEMM point, next to cuBLAS-class numbers
+        n = 8192
+        dt = torch.bfloat16 if name == "gemm_bf16" else torch.float32
+        g.manual_seed(6)
+        a = torch.randn(n, n, generator=g).to(dt).to(dev)
+        b = torch.randn(n, n, generator=g).to(dt).to(dev)  # [N, K]: torch Linear layout
+        c = torch.empty(n, n, dtype=dt, device=dev)
+
+        def step():
+            ops.gemm(a, b, c, transb=True)
+
+        return dict(step=step, units=2 * n ** 3, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops",
+                    dtype="bf16" if name == "gemm_bf16" else "f32(split-bf16x3)", bound="tensor",
+                    peak=peaks["bf16_tflops"] / (1 if name == "gemm_bf16" else 3), launches_per_step=1,
+                    config={"workload": f"GEMM {name[5:]} 8192^3, B as [N,K]", "l2": "operands (128-256 MB each) larger than L2"},
+                    kind="gemm", replicas_only=True)
+
     if name in ("conv_f32", "conv_bf16"):
         n_total = 32
         n_local = n_total // world if world > 1 else n_total
@@ -343,6 +361,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the e2e and CPU-baseline legs (profiling runs)")
     ap.add_argument("--extra-steps", type=int, default=10)
     args = ap.parse_args()
 
@@ -384,14 +403,14 @@ def main():
             "scaling": "replicas" if wl.get("replicas_only") else "weak", "vs_baseline": None, "dtype": wl["dtype"],
             "data": "synthetic", "config": wl["config"], "roofline": roof, "gpu_launches": int(launches), "clocks": clocks}
 
-    if args.workload == "softmax":
+    if args.workload == "softmax" and not args.kernel_only:
         line["e2e"] = e2e_softmax(torch, dist, ops, max(args.steps // 5, 5), args.warmup, world)
         if rank == 0 and world == 1:
             line["cpu_baseline"] = {k: v for k, v in cpu_softmax_baseline().items() if k != "ms_per_step"}
 
     if not args.no_extras and args.workload == "softmax":
         extras = []
-        names = ["gemm_f64", "conv_f32", "conv_bf16", "attention", "attention_causal", "block_f32", "block_bf16"]
+        names = ["gemm_f64", "gemm_bf16", "gemm_f32", "conv_f32", "conv_bf16", "attention", "attention_causal", "block_f32", "block_bf16"]
         for nm in names:
             try:
                 w2 = make_workload(nm, torch, ops, rank, world)

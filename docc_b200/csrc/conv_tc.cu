@@ -1,10 +1,380 @@
-// Implicit-GEMM convolution on the tcgen05 engine.
+// Implicit-GEMM 2-D convolution (stride 1, dilation 1, one group) on tcgen05.
+//
+// docc's expansion of ConvNode (conv_node.cpp:243-399) gives every output element its own
+// sequential C_in*kh*kw FMA chain. Here, per image,  Y_n[oc, pixel] = sum_{tap, c} W[oc, tap, c] *
+// X_n[pixel + tap, c]  is a GEMM with M = C_out, N = output pixels, K = kh*kw*C_in:
+//   1. one pass re-lays X from NCHW to NHWC 16-bit (fp32 input: bf16 hi and lo planes) and W from
+//      [oc][c][kh][kw] to [oc][kh][kw][c], so that K is contiguous for both operands;
+//   2. a persistent warp-specialised kernel (same skeleton as the GEMM engine: TMA producer warp,
+//      UMMA issuer warp, four epilogue warps, two TMEM accumulators) walks tiles of 128 output
+//      channels x up to four output rows. For each filter tap the producer issues one TMA load per
+//      output row with the tap's (kh - pad, kw - pad) shift in the *outer* coordinates; rows and
+//      columns that fall outside the image are zero-filled by TMA, which is the zero padding.
+//   3. the accumulator tile is [oc lanes x pixel columns], i.e. already NCHW: every lane streams its
+//      channel's pixels straight to Y with the bias added.
+// fp32 inputs run three passes (w_lo*x_hi, w_hi*x_lo, w_hi*x_hi) into the same accumulator.
 #include "conv.h"
+#include "device_math.cuh"
+#include "gemm_tc.h"
+#include "ptx.cuh"
 
 namespace docc_b200 {
+namespace {
 
-int conv_tc(Ctx*, const ConvTcProblem&, const void*, const void*, const float*, float*) {
-    return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: not available");
+using namespace ptx;
+
+constexpr int kThreads = 192;
+constexpr uint32_t kABytes = 128 * 64 * 2;
+constexpr uint32_t kBBytes = 256 * 64 * 2;
+constexpr int kStages = 4;
+constexpr uint32_t kTmemCols = 512;
+
+struct ConvKernelParams {
+    int N, C, H, W, c_out, kh, kw, pad_h, pad_w, Ho, Wo;
+    int npass;
+    int pw[3], px[3];  // weight / input plane used by each pass
+    int r_max;         // output rows per tile (r_max * Wo <= 256)
+    int tiles_m;
+    long long total_units;  // tiles_m * N * Ho output-row units
+    const float* bias;
+    float* Y;
+    DeviceStatus* status;
+};
+
+__device__ __forceinline__ void conv_timeout(DeviceStatus* st, unsigned where) {
+    volatile unsigned int* f = &st->timeout_flag;
+    volatile unsigned int* w = &st->timeout_where;
+    if (*w == 0u) *w = where;
+    *f = 1u;
+    __threadfence_system();
+}
+
+struct Tile {
+    int m0, n, oh0, rows;
+};
+
+// Work is the list of (channel tile, image, output row) units; CTA i owns the contiguous range
+// [i*U/G, (i+1)*U/G) and cuts it into tiles of at most r_max rows inside one image.
+__device__ __forceinline__ bool next_tile(const ConvKernelParams& p, long long& u, long long u_end, Tile& t) {
+    if (u >= u_end) return false;
+    const long long rows_total = (long long)p.N * p.Ho;
+    const long long mt = u / rows_total;
+    const long long row = u - mt * rows_total;
+    t.m0 = int(mt) * 128;
+    t.n = int(row / p.Ho);
+    t.oh0 = int(row - (long long)t.n * p.Ho);
+    // rows still to do in this image and range, cut into equal tiles of at most r_max rows
+    long long rem = p.Ho - t.oh0;
+    if (rem > u_end - u) rem = u_end - u;
+    const long long nt = (rem + p.r_max - 1) / p.r_max;
+    const long long r = (rem + nt - 1) / nt;
+    t.rows = int(r);
+    u += r;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    conv_tc_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+                   const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmX1,
+                   const ConvKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sA = base;
+    const uint32_t sB = sA + kStages * kABytes;
+    const uint32_t bars = sB + kStages * kBBytes;
+    auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
+    auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
+    auto tfull_bar = [&](int i) { return bars + 128u + 8u * uint32_t(i); };
+    auto tempty_bar = [&](int i) { return bars + 144u + 8u * uint32_t(i); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 160u - raw_addr));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < kStages; i++) {
+            mbar_init(full_bar(i), 1);
+            mbar_init(empty_bar(i), 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(tfull_bar(i), 1);
+            mbar_init(tempty_bar(i), 4);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmW0);
+        prefetch_tensormap(&tmX0);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const long long u_begin = p.total_units * blockIdx.x / gridDim.x;
+    const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
+    const int cblocks = p.C / 64;
+    const int kb_per_pass = p.kh * p.kw * cblocks;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            while (ok && next_tile(p, u, u_end, t)) {
+                const uint32_t tx = kABytes + uint32_t(t.rows) * uint32_t(p.Wo) * 128u;
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    const CUtensorMap* mw = p.pw[pass] ? &tmW1 : &tmW0;
+                    const CUtensorMap* mx = p.px[pass] ? &tmX1 : &tmX0;
+                    for (int kb = 0; kb < kb_per_pass; kb++, it++) {
+                        const int s = int(it % kStages);
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+                            conv_timeout(p.status, 21);
+                            ok = false;
+                            break;
+                        }
+                        const int tap = kb / cblocks, cb = kb - tap * cblocks;
+                        const int ky = tap / p.kw, kx = tap - ky * p.kw;
+                        mbar_arrive_expect_tx(full_bar(s), tx);
+                        tma_load_2d(sA + uint32_t(s) * kABytes, mw, full_bar(s), kb * 64, t.m0);
+                        const uint32_t b_dst = sB + uint32_t(s) * kBBytes;
+                        for (int r = 0; r < t.rows; r++)
+                            tma_load_4d(b_dst + uint32_t(r) * uint32_t(p.Wo) * 128u, mx, full_bar(s), cb * 64, kx - p.pad_w,
+                                        t.oh0 + r + ky - p.pad_h, t.n);
+                    }
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t it = 0, lt = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            while (ok && next_tile(p, u, u_end, t)) {
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                lt++;
+                if (!mbar_wait(tempty_bar(int(buf)), (use & 1u) ^ 1u)) {
+                    conv_timeout(p.status, 22);
+                    break;
+                }
+                tc_fence_after();
+                const int n_mma = (t.rows * p.Wo + 15) / 16 * 16;
+                const uint32_t idesc = make_idesc(128, n_mma, 1, 0, 0);
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    for (int kb = 0; kb < kb_per_pass; kb++, it++) {
+                        const int s = int(it % kStages);
+                        const uint32_t ph = (it / kStages) & 1u;
+                        if (!mbar_wait(full_bar(s), ph)) {
+                            conv_timeout(p.status, 23);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t a_base = sA + uint32_t(s) * kABytes, b_base = sB + uint32_t(s) * kBBytes;
+#pragma unroll
+                        for (int kk = 0; kk < 4; kk++) {
+                            umma_f16_ss(d_tmem, make_smem_desc(a_base + uint32_t(kk) * 32u, 16u, 1024u),
+                                        make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u), idesc, acc);
+                            acc = 1;
+                        }
+                        umma_commit(empty_bar(s));
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(int(buf)));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        uint32_t lt = 0;
+        long long u = u_begin;
+        Tile t;
+        const long long plane = (long long)p.Ho * p.Wo;
+        while (next_tile(p, u, u_end, t)) {
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            lt++;
+            if (!mbar_wait(tfull_bar(int(buf)), use & 1u)) {
+                if (lane == 0) conv_timeout(p.status, 24);
+                break;
+            }
+            tc_fence_after();
+            const int oc = t.m0 + q * 32 + lane;
+            const int ncols = t.rows * p.Wo;
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
+            const bool row_ok = oc < p.c_out;
+            const float bv = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.f;
+            float* yrow = p.Y + ((long long)t.n * p.c_out + (row_ok ? oc : 0)) * plane + (long long)t.oh0 * p.Wo;
+            const bool vec = (reinterpret_cast<uintptr_t>(yrow) & 15) == 0;
+            for (int c = 0; c < ncols; c += 16) {
+                uint32_t r[16];
+                tmem_ld_x16(t_addr + uint32_t(c), r);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                if (vec && c + 16 <= ncols) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        float4 o;
+                        o.x = __uint_as_float(r[v4 * 4 + 0]) + bv;
+                        o.y = __uint_as_float(r[v4 * 4 + 1]) + bv;
+                        o.z = __uint_as_float(r[v4 * 4 + 2]) + bv;
+                        o.w = __uint_as_float(r[v4 * 4 + 3]) + bv;
+                        __stcs(reinterpret_cast<float4*>(yrow + c) + v4, o);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (c + j < ncols) yrow[c + j] = __uint_as_float(r[j]) + bv;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(int(buf)));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- layout pre-passes ---------------------------------------------------------------------------
+template <typename TIn> __device__ __forceinline__ float ld_f(const TIn* p) { return to_float(*p); }
+
+// X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16. 32x32 tiles through shared memory.
+template <typename TIn, bool SPLIT>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ X, __nv_bfloat16* __restrict__ hi,
+                                                           __nv_bfloat16* __restrict__ lo, int C, long long HW) {
+    __shared__ float tile[32][33];
+    const long long n = blockIdx.z;
+    const long long p0 = (long long)blockIdx.x * 32;
+    const int c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const TIn* xin = X + n * C * HW;
+    for (int j = ty; j < 32; j += 8) {
+        const int c = c0 + j;
+        const long long px = p0 + tx;
+        tile[j][tx] = (c < C && px < HW) ? ld_f(xin + c * HW + px) : 0.f;
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        const long long px = p0 + j;
+        const int c = c0 + tx;
+        if (px < HW && c < C) {
+            const float v = tile[tx][j];
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            const long long o = (n * HW + px) * C + c;
+            hi[o] = h;
+            if (SPLIT) lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
+        }
+    }
+}
+
+// W [oc][c][taps] -> hi (and lo) [oc][taps][c]
+template <typename TIn, bool SPLIT>
+__global__ void __launch_bounds__(256) weight_relayout_kernel(const TIn* __restrict__ Wt, __nv_bfloat16* __restrict__ hi,
+                                                              __nv_bfloat16* __restrict__ lo, int c_out, int C, int taps) {
+    const long long total = (long long)c_out * C * taps;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = int(i % C);
+        const int tap = int((i / C) % taps);
+        const long long oc = i / ((long long)C * taps);
+        const float v = ld_f(Wt + (oc * C + c) * taps + tap);
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        if (SPLIT) lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
+bool g_conv_attr[16] = {false};
+
+}  // namespace
+
+int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, const float* bias, float* Y) {
+    if (q.C % 64 != 0 || q.C <= 0) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: C_in %% 64 != 0");
+    if (q.Wo < 1 || q.Wo > 256 || q.Ho < 1) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: output width outside [1,256]");
+    if (q.N > INT32_MAX || q.H > 65535 || q.W > 65535 || q.c_out > INT32_MAX / 2 || q.kh * q.kw * q.C > INT32_MAX / 2)
+        return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: extent too large");
+    const bool split = q.prec_in == DOCC_B200_PREC_S;
+    const int planes = split ? 2 : 1;
+    const int64_t HW = q.H * q.W, taps = q.kh * q.kw, Kt = taps * q.C;
+    const size_t x_elems = size_t(q.N) * HW * q.C, w_elems = size_t(q.c_out) * Kt;
+    void *wx, *ww;
+    DOCC_TRY(get_workspace(ctx, 0, x_elems * planes * 2, &wx));
+    DOCC_TRY(get_workspace(ctx, 1, w_elems * planes * 2 + 256, &ww));
+    __nv_bfloat16* x_hi = static_cast<__nv_bfloat16*>(wx);
+    __nv_bfloat16* x_lo = x_hi + x_elems;
+    __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
+    __nv_bfloat16* w_lo = w_hi + (w_elems + 63) / 64 * 64;
+
+    {
+        dim3 grid(unsigned(ceil_div(HW, 32)), unsigned(ceil_div(q.C, 32)), unsigned(q.N));
+        if (grid.z > 65535) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: batch too large");
+        if (split) nchw_to_nhwc_kernel<float, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW);
+        else nchw_to_nhwc_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW);
+        DOCC_TRY(after_launch(ctx, "nchw_to_nhwc_kernel"));
+        int64_t blocks = ceil_div(int64_t(w_elems), 256);
+        if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+        if (split) weight_relayout_kernel<float, true><<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(Wt), w_hi, w_lo, int(q.c_out), int(q.C), int(taps));
+        else weight_relayout_kernel<__nv_bfloat16, false><<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(q.C), int(taps));
+        DOCC_TRY(after_launch(ctx, "weight_relayout_kernel"));
+    }
+
+    CUtensorMap maps[4];
+    memset(maps, 0, sizeof(maps));
+    for (int i = 0; i < 2; i++) {
+        const __nv_bfloat16* wp = (i == 1 && split) ? w_lo : w_hi;
+        const __nv_bfloat16* xp = (i == 1 && split) ? x_lo : x_hi;
+        const uint64_t wd[2] = {uint64_t(Kt), uint64_t(q.c_out)};
+        const uint64_t ws[1] = {uint64_t(Kt) * 2};
+        const uint32_t wb[2] = {64, 128};
+        DOCC_TRY(encode_tmap_16bit(&maps[i], wp, 2, wd, ws, wb));
+        const uint64_t xd[4] = {uint64_t(q.C), uint64_t(q.W), uint64_t(q.H), uint64_t(q.N)};
+        const uint64_t xs[3] = {uint64_t(q.C) * 2, uint64_t(q.W) * q.C * 2, uint64_t(HW) * q.C * 2};
+        const uint32_t xb[4] = {64, uint32_t(q.Wo), 1, 1};
+        DOCC_TRY(encode_tmap_16bit(&maps[2 + i], xp, 4, xd, xs, xb));
+    }
+
+    ConvKernelParams p;
+    memset(&p, 0, sizeof(p));
+    p.N = int(q.N); p.C = int(q.C); p.H = int(q.H); p.W = int(q.W); p.c_out = int(q.c_out);
+    p.kh = int(q.kh); p.kw = int(q.kw); p.pad_h = int(q.pad_h); p.pad_w = int(q.pad_w); p.Ho = int(q.Ho); p.Wo = int(q.Wo);
+    if (split) {
+        p.npass = 3;  // small terms first
+        p.pw[0] = 1; p.px[0] = 0;
+        p.pw[1] = 0; p.px[1] = 1;
+        p.pw[2] = 0; p.px[2] = 0;
+    } else {
+        p.npass = 1;
+    }
+    p.r_max = int(256 / q.Wo);
+    if (p.r_max > 8) p.r_max = 8;
+    p.tiles_m = int(ceil_div(q.c_out, 128));
+    p.total_units = (long long)p.tiles_m * q.N * q.Ho;
+    p.bias = bias; p.Y = Y; p.status = ctx->status_dev;
+
+    const size_t smem = size_t(kStages) * (kABytes + kBBytes) + 1024 + 256;
+    if (!g_conv_attr[ctx->device & 15]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        g_conv_attr[ctx->device & 15] = true;
+    }
+    // enough CTAs that each gets at least one full tile; never more than one per SM
+    long long grid = ceil_div(p.total_units, p.r_max);
+    if (grid > ctx->sm_count) grid = ctx->sm_count;
+    conv_tc_kernel<<<unsigned(grid), kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    return after_launch(ctx, "conv_tc_kernel");
 }
 
 }  // namespace docc_b200
