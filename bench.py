@@ -29,6 +29,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+from docc_b200.sharding import gather_shards, shard  # noqa: E402
+
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -162,9 +164,9 @@ def make_workload(name, torch, ops, rank, world):
 
     if name in ("conv_f32", "conv_bf16"):
         n_total = 32
-        n_local = n_total // world if world > 1 else n_total
         g.manual_seed(2)
-        x = torch.randn(n_total, 64, 56, 56, generator=g)[rank * n_local:(rank + 1) * n_local]
+        x = shard(torch.randn(n_total, 64, 56, 56, generator=g), rank, world)
+        n_local = x.shape[0]
         w = torch.nn.init.kaiming_normal_(torch.empty(128, 64, 3, 3), generator=g)
         bias = torch.zeros(128)
         if name == "conv_bf16":
@@ -180,15 +182,14 @@ def make_workload(name, torch, ops, rank, world):
                     dtype="bf16" if name == "conv_bf16" else "f32(split-bf16x3)", bound="tensor",
                     peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None,
                     config={"workload": f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)",
-                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv", gather=True)
+                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv", gather=n_total)
 
     if name in ("attention", "attention_causal"):
         causal = name.endswith("causal")
         bh_total = 8
-        b_local = bh_total // world if world > 1 else bh_total
         g.manual_seed(3)
-        q, k, v = (torch.randn(bh_total, 16, 2048, 128, generator=g)[rank * b_local:(rank + 1) * b_local].bfloat16().to(dev)
-                   for _ in range(3))
+        q, k, v = (shard(torch.randn(bh_total, 16, 2048, 128, generator=g), rank, world).bfloat16().to(dev) for _ in range(3))
+        b_local = q.shape[0]
 
         def step():
             return ops.attention(q, k, v, causal=causal)
@@ -198,12 +199,11 @@ def make_workload(name, torch, ops, rank, world):
                     bound="tensor", peak=peaks["bf16_tflops"], launches_per_step=1,
                     config={"workload": f"attention bf16 [8,16,2048,128] causal={causal} (BASELINE config 4)",
                             "batch_per_gpu": b_local, "l2": "flushed between steps"}, flush=True, kind="attention",
-                    gather=True)
+                    gather=bh_total)
 
     if name in ("block_f32", "block_bf16"):
         bf = name.endswith("bf16")
         b_total = 32
-        b_local = b_total // world if world > 1 else b_total
         d, heads, dff, seq = 1024, 16, 4096, 512
         torch.manual_seed(4)
         p = {"ln1_g": torch.ones(d), "ln1_b": torch.zeros(d), "ln2_g": torch.ones(d), "ln2_b": torch.zeros(d)}
@@ -211,7 +211,8 @@ def make_workload(name, torch, ops, rank, world):
             p[nm] = torch.nn.init.xavier_uniform_(torch.empty(*shp))
         for nm, n in (("b_qkv", 3 * d), ("b_o", d), ("b_1", dff), ("b_2", d)):
             p[nm] = torch.zeros(n)
-        x = torch.randn(b_total, seq, d)[rank * b_local:(rank + 1) * b_local]
+        x = shard(torch.randn(b_total, seq, d), rank, world)
+        b_local = x.shape[0]
         small = ("ln1_g", "ln1_b", "ln2_g", "ln2_b", "b_qkv", "b_o", "b_1", "b_2")
         pd = {k_: (v_.to(dev) if (k_ in small or not bf) else v_.bfloat16().to(dev)) for k_, v_ in p.items()}
         x = (x.bfloat16() if bf else x).to(dev)
@@ -226,7 +227,7 @@ def make_workload(name, torch, ops, rank, world):
                     peak=peaks["bf16_tflops_sustained"] / (1 if bf else 3), launches_per_step=None,
                     config={"workload": f"pre-LN encoder block {'bf16' if bf else 'fp32'} d1024 h16 ff4096 [32,512,1024] "
                                         "(BASELINE config 5)", "batch_per_gpu": b_local, "l2": "flushed between steps"},
-                    flush=True, kind="block", gather=True)
+                    flush=True, kind="block", gather=b_total)
 
     raise SystemExit(f"unknown workload {name}")
 
@@ -235,15 +236,10 @@ def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clock
     """Device-timed loop: W warm-ups, then K steps bracketed by barrier + synchronize, max over ranks."""
     dev_index = torch.cuda.current_device()
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if wl.get("flush") else None
-    gather_out = None
-
     def one_step():
         out = wl["step"]()
         if world > 1 and wl.get("gather") and out is not None:
-            nonlocal gather_out
-            if gather_out is None:
-                gather_out = torch.empty((world * out.shape[0],) + tuple(out.shape[1:]), dtype=out.dtype, device=out.device)
-            dist.all_gather_into_tensor(gather_out, out)
+            gather_shards(out, wl["gather"])  # the one collective: NCCL all-gather of the output shards
 
     for _ in range(max(warmup, 3)):
         one_step()

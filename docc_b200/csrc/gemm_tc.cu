@@ -4,16 +4,18 @@
 // Replaces the cublas{S,D}gemm call sequence of docc's CUDA target
 // (opt/src/targets/cuda/blas/gemm.cpp:131-185) for everything except fp64.
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of 128x64 A tiles and BNx64 B tiles into a
 //               ring of 128-byte-swizzled shared-memory stages, completion on mbarriers.
 //   warp 1      UMMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=16) four times per stage;
 //               tcgen05.commit releases the stage and, after the last k-block, publishes the
 //               accumulator. It also owns the tensor-memory allocation.
-//   warps 2-5   epilogue: tcgen05.ld the 128xBN fp32 accumulator (each warp its own 32-lane
-//               quadrant), apply alpha/beta/bias/activation/residual, store.
-// Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop
-// of tile i+1. fp32 operands are handled as split bf16 (hi + lo): the kernel runs up to three
+//   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (each warp its own 32-lane quadrant),
+//               apply alpha/beta/bias/activation/residual, store.
+// Tiles are 256xBN (two M=128 UMMAs per k-step sharing the B tile; both 256-column TMEM regions
+// belong to one tile and each epilogue warp group drains one of them) or 128xBN (the two TMEM
+// regions are alternating accumulator buffers, so the epilogue of tile i overlaps the main loop
+// of tile i+1). fp32 operands are handled as split bf16 (hi + lo): the kernel runs up to three
 // passes (hi*hi, hi*lo, lo*hi) into the same accumulator, which keeps fp32-level accuracy
 // (~2^-16 relative per product) at a third of the bf16 rate. Every wait is bounded.
 #include <mutex>
@@ -27,10 +29,8 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 192;
-constexpr uint32_t kABytes = kBM * kBK * 2;
+constexpr int kThreads = 320;  // TMA warp, UMMA warp, eight epilogue warps
 constexpr int kMaxStages = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kSmemBudget = 227 * 1024;
@@ -39,7 +39,9 @@ struct TcKernelParams {
     int M, N, K, batch;
     int npass;
     int pa[3], pb[3];
-    int bn;
+    int bm, bn;  // tile: bm is 128 or 256 rows
+    int group_m;  // row tiles per group of the tile order
+    uint32_t a_bytes;
     int a_kmajor, b_kmajor;
     int a_bcast, b_bcast;  // operand shared by all batch items
     int tiles_m, tiles_n;
@@ -130,6 +132,22 @@ __device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const ui
     }
 }
 
+// Tile coordinates of linear tile index t. Tiles are walked in groups of `group_m` row tiles
+// (m fastest inside a group), so that the ~148 tiles in flight cover a near-square patch of C and
+// the operand panels they share stay in L2.
+__device__ __forceinline__ void tile_coords(const TcKernelParams& p, int t, int& b, int& m0, int& n0) {
+    const int tiles_per_batch = p.tiles_m * p.tiles_n;
+    b = t / tiles_per_batch;
+    const int rem = t - b * tiles_per_batch;
+    const int per_group = p.group_m * p.tiles_n;
+    const int g = rem / per_group;
+    const int first_m = g * p.group_m;
+    const int gm = p.tiles_m - first_m < p.group_m ? p.tiles_m - first_m : p.group_m;
+    const int in_group = rem - g * per_group;
+    m0 = (first_m + in_group % gm) * p.bm;
+    n0 = (in_group / gm) * p.bn;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
     tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
@@ -138,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     const uint32_t sA = base;
-    const uint32_t sB = sA + uint32_t(p.stages) * kABytes;
+    const uint32_t sB = sA + uint32_t(p.stages) * p.a_bytes;
     const uint32_t bars = sB + uint32_t(p.stages) * p.b_bytes;
     auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
     auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
@@ -148,6 +166,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // bm == 256: one tile owns both TMEM regions (rows 0-127 in columns [0,256), rows 128-255 in
+    // [256,512)); bm == 128: the regions are two accumulator buffers used by alternate tiles.
+    const bool tall = p.bm == 256;
 
     if (warp == 0 && lane == 0) {
         for (int i = 0; i < p.stages; i++) {
@@ -156,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(tfull_bar(i), 1);
-            mbar_init(tempty_bar(i), 4);
+            mbar_init(tempty_bar(i), tall ? 4 : 8);  // one arrival per epilogue warp that drains the region
         }
         fence_barrier_init();
         prefetch_tensormap(&tmA0);
@@ -175,9 +196,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    const int tiles_per_batch = p.tiles_m * p.tiles_n;
-    const int total_tiles = tiles_per_batch * p.batch;
-    const uint32_t stage_tx = kABytes + uint32_t(p.bn) * 128u;
+    const int total_tiles = p.tiles_m * p.tiles_n * p.batch;
+    const uint32_t stage_tx = p.a_bytes + uint32_t(p.bn) * 128u;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -185,10 +205,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int b = t / tiles_per_batch;
-                const int rem = t - b * tiles_per_batch;
-                const int n0 = (rem / p.tiles_m) * p.bn;
-                const int m0 = (rem % p.tiles_m) * kBM;
+                int b, m0, n0;
+                tile_coords(p, t, b, m0, n0);
                 const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
                 for (int pass = 0; pass < p.npass && ok; pass++) {
                     const CUtensorMap* ma = p.pa[pass] ? &tmA1 : &tmA0;
@@ -202,14 +220,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                             break;
                         }
                         mbar_arrive_expect_tx(full_bar(s), stage_tx);
-                        const uint32_t a_dst = sA + uint32_t(s) * kABytes;
+                        const uint32_t a_dst = sA + uint32_t(s) * p.a_bytes;
                         const uint32_t b_dst = sB + uint32_t(s) * p.b_bytes;
                         const int k0 = kb * kBK;
                         if (p.a_kmajor) {
                             tma_load_3d(a_dst, ma, full_bar(s), k0, m0, ba);
                         } else {
-                            tma_load_3d(a_dst, ma, full_bar(s), m0, k0, ba);
-                            tma_load_3d(a_dst + 8192u, ma, full_bar(s), m0 + 64, k0, ba);
+                            for (int j = 0; j < p.bm / 64; j++)
+                                tma_load_3d(a_dst + uint32_t(j) * 8192u, ma, full_bar(s), m0 + 64 * j, k0, ba);
                         }
                         if (p.b_kmajor) {
                             tma_load_3d(b_dst, mb, full_bar(s), k0, n0, bb);
@@ -233,18 +251,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t it = 0;
             uint32_t lt = 0;
             bool ok = true;
+            const int halves = tall ? 2 : 1;
+            const int last_it = p.npass * p.num_kb - 1;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
-                const uint32_t buf = lt & 1u;
-                const uint32_t use = lt >> 1;
-                if (!mbar_wait(tempty_bar(int(buf)), (use & 1u) ^ 1u)) {
-                    report_timeout(p.status, 2);
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * 256u;
-                uint32_t acc = 0;
+                const uint32_t buf = tall ? 0u : (lt & 1u);
+                const uint32_t wait_parity = tall ? ((lt & 1u) ^ 1u) : (((lt >> 1) & 1u) ^ 1u);
+                int local_it = 0;
                 for (int pass = 0; pass < p.npass && ok; pass++) {
-                    for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                    for (int kb = 0; kb < p.num_kb; kb++, it++, local_it++) {
                         const int s = int(it % uint32_t(p.stages));
                         const uint32_t ph = (it / uint32_t(p.stages)) & 1u;
                         if (!mbar_wait(full_bar(s), ph)) {
@@ -253,42 +267,59 @@ __global__ void __launch_bounds__(kThreads, 1)
                             break;
                         }
                         tc_fence_after();
-                        const uint32_t a_base = sA + uint32_t(s) * kABytes;
+                        const uint32_t a_base = sA + uint32_t(s) * p.a_bytes;
                         const uint32_t b_base = sB + uint32_t(s) * p.b_bytes;
+                        for (int h = 0; h < halves && ok; h++) {
+                            const uint32_t region = tall ? uint32_t(h) : buf;
+                            if (local_it == 0) {
+                                // the epilogue must have drained this TMEM region before it is overwritten
+                                if (!mbar_wait(tempty_bar(int(region)), wait_parity)) {
+                                    report_timeout(p.status, 2);
+                                    ok = false;
+                                    break;
+                                }
+                                tc_fence_after();
+                            }
+                            const uint32_t d_tmem = tmem_base + region * 256u;
+                            const uint32_t a_half = a_base + uint32_t(h) * 16384u;  // 128 rows of either A layout
 #pragma unroll
-                        for (int kk = 0; kk < kBK / 16; kk++) {
-                            const uint64_t da = p.a_kmajor ? make_smem_desc(a_base + uint32_t(kk) * 32u, 16u, 1024u)
-                                                           : make_smem_desc(a_base + uint32_t(kk) * 2048u, 8192u, 1024u);
-                            const uint64_t db = p.b_kmajor ? make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u)
-                                                           : make_smem_desc(b_base + uint32_t(kk) * 2048u, 8192u, 1024u);
-                            umma_f16_ss(d_tmem, da, db, p.idesc, acc);
-                            acc = 1;
+                            for (int kk = 0; kk < kBK / 16; kk++) {
+                                const uint64_t da = p.a_kmajor ? make_smem_desc(a_half + uint32_t(kk) * 32u, 16u, 1024u)
+                                                               : make_smem_desc(a_half + uint32_t(kk) * 2048u, 8192u, 1024u);
+                                const uint64_t db = p.b_kmajor ? make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u)
+                                                               : make_smem_desc(b_base + uint32_t(kk) * 2048u, 8192u, 1024u);
+                                umma_f16_ss(d_tmem, da, db, p.idesc, (local_it > 0 || kk > 0) ? 1u : 0u);
+                            }
+                            if (local_it == last_it) umma_commit(tfull_bar(int(region)));  // accumulator region complete
                         }
+                        if (!ok) break;
                         umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
                     }
                 }
-                if (ok) umma_commit(tfull_bar(int(buf)));
             }
         }
     } else {
-        // ---------------- epilogue warps ----------------
-        const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+        // ---------------- epilogue warps (two groups of four) ----------------
+        const int q = warp & 3;          // tensor-memory lane quadrant this warp may read
+        const int wg = (warp - 2) >> 2;  // 0 or 1
         uint32_t lt = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, lt++) {
-            const uint32_t buf = lt & 1u;
-            const uint32_t use = lt >> 1;
-            const int b = t / tiles_per_batch;
-            const int rem = t - b * tiles_per_batch;
-            const int n0 = (rem / p.tiles_m) * p.bn;
-            const int m0 = (rem % p.tiles_m) * kBM;
-            if (!mbar_wait(tfull_bar(int(buf)), use & 1u)) {
+            int b, m0, n0;
+            tile_coords(p, t, b, m0, n0);
+            const uint32_t region = tall ? uint32_t(wg) : (lt & 1u);
+            const uint32_t parity = tall ? (lt & 1u) : ((lt >> 1) & 1u);
+            if (!mbar_wait(tfull_bar(int(region)), parity)) {
                 if (lane == 0) report_timeout(p.status, 4);
                 break;
             }
             tc_fence_after();
-            const long long row = m0 + q * 32 + lane;
-            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
-            for (int c = 0; c < p.bn; c += 16) {
+            const long long row = m0 + (tall ? wg * 128 : 0) + q * 32 + lane;
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + region * 256u;
+            // tall tiles: each group drains its own 128 rows; otherwise the groups split the columns
+            const int half_cols = ((p.bn / 2) + 15) / 16 * 16;
+            const int c_begin = tall ? 0 : (wg == 0 ? 0 : half_cols);
+            const int c_end = tall ? p.bn : (wg == 0 ? half_cols : p.bn);
+            for (int c = c_begin; c < c_end; c += 16) {
                 uint32_t r[16];
                 tmem_ld_x16(t_addr + uint32_t(c), r);
                 tmem_ld_wait();
@@ -300,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(int(buf)));
+            if (lane == 0) mbar_arrive(tempty_bar(int(region)));
         }
     }
 
@@ -486,29 +517,47 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
     p.a_bcast = (batch > 1 && A[0].batch_stride == 0) ? 1 : 0;
     p.b_bcast = (batch > 1 && B[0].batch_stride == 0) ? 1 : 0;
 
-    // N tile: the largest of 256/128/64 that still yields at least one tile per SM; MN-major B
-    // needs multiples of 64, small N uses the next multiple of 16.
-    const int64_t tiles_m = ceil_div(M, kBM);
-    int bn;
+    // Tile shape. L2 feeds an SM at most ~64 B/clk, so the tensor pipe only stays busy when a
+    // k-block's flops per loaded byte are high: 256x256 tiles (131 flop/B) run at full rate,
+    // 128x256 at ~0.68, 128x128 at ~0.5. Small problems prefer more, smaller tiles. Pick the
+    // candidate with the lowest (waves x tile area / efficiency).
+    int bm = 128, bn;
     if (N <= 64) {
         bn = p.b_kmajor ? int(ceil_div(N, 16) * 16) : 64;
     } else {
-        bn = 256;
-        while (bn > 64 && (bn / 2 >= N || tiles_m * ceil_div(N, bn) * batch < ctx->sm_count)) bn /= 2;
-        if (bn > 64 && N <= bn / 2) bn /= 2;
+        static const struct { int bm, bn; double eff; } cand[] = {{256, 256, 1.0}, {128, 256, 0.68}, {128, 128, 0.5}, {128, 64, 0.33}};
+        double best = 0;
+        bn = 64;
+        for (const auto& c : cand) {
+            if (c.bm == 256 && M <= 128) continue;
+            // a 256-row tile owns all of TMEM, so its epilogue does not overlap the next main loop:
+            // only worth it when the main loop is long
+            if (c.bm == 256 && K * npass < 2048) continue;
+            if (c.bn > 64 && c.bn / 2 >= N) continue;
+            const int64_t tiles = ceil_div(M, c.bm) * ceil_div(N, c.bn) * batch;
+            const double cost = double(ceil_div(tiles, ctx->sm_count)) * c.bm * c.bn / c.eff;
+            if (best == 0 || cost < best) {
+                best = cost;
+                bm = c.bm;
+                bn = c.bn;
+            }
+        }
     }
+    p.bm = bm;
     p.bn = bn;
-    p.tiles_m = int(tiles_m);
+    p.a_bytes = uint32_t(bm) * 128u;
+    p.tiles_m = int(ceil_div(M, bm));
     p.tiles_n = int(ceil_div(N, bn));
+    p.group_m = bm == 256 ? 12 : 16;
     p.num_kb = int(ceil_div(K, kBK));
     p.b_bytes = uint32_t((bn * 128 + 1023) / 1024 * 1024);
-    int stages = (kSmemBudget - 2048) / int(kABytes + p.b_bytes);
+    int stages = (kSmemBudget - 2048) / int(p.a_bytes + p.b_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     const int64_t k_iters = int64_t(p.num_kb) * npass;
     if (stages > k_iters && k_iters >= 2) stages = int(k_iters);
     if (stages < 2) stages = 2;
     p.stages = stages;
-    p.idesc = make_idesc(kBM, bn, ab_format, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+    p.idesc = make_idesc(128, bn, ab_format, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
 
     p.alpha = ep.alpha; p.beta = ep.beta;
     p.bias = ep.bias; p.bias_mode = ep.bias ? ep.bias_mode : 0;
@@ -543,11 +592,11 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         return encode_tmap_16bit(m, o.ptr, 3, dims, strides, box);
     };
     for (int i = 0; i < 2; i++) {
-        DOCC_TRY(encode_operand(&maps[i], A[i < n_a ? i : 0], M, kBM, p.a_bcast || batch == 1));
+        DOCC_TRY(encode_operand(&maps[i], A[i < n_a ? i : 0], M, uint32_t(bm), p.a_bcast || batch == 1));
         DOCC_TRY(encode_operand(&maps[2 + i], B[i < n_b ? i : 0], N, uint32_t(bn), p.b_bcast || batch == 1));
     }
 
-    const size_t smem = size_t(stages) * (kABytes + p.b_bytes) + 1024 + 256;
+    const size_t smem = size_t(stages) * (p.a_bytes + p.b_bytes) + 1024 + 256;
     if (!g_attr_set[ctx->device & 15]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
         g_attr_set[ctx->device & 15] = true;

@@ -26,6 +26,71 @@ _i64 = ctypes.c_int64
 _vp = ctypes.c_void_p
 
 
+class DeviceArray:
+    """A C-order array in device memory obtained from ``docc_b200_malloc`` (the runtime's pool).
+
+    This is what a container of an offloaded SDFG is between its H2D and D2H transfer nodes: the
+    front ends keep intermediates in DeviceArrays so that consecutive library nodes exchange no
+    data with the host. Freed through ``docc_b200_free`` when the last reference goes away."""
+
+    is_cuda = True
+
+    def __init__(self, shape, dtype):
+        self.shape = tuple(int(v) for v in shape)
+        self.dtype = np.dtype(dtype)
+        self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize if self.shape else self.dtype.itemsize
+        ptr = _vp()
+        call("docc_b200_malloc", ctypes.byref(ptr), max(self.nbytes, 1))
+        self._ptr = ptr.value
+        self._owner = None
+
+    @property
+    def ndim(self):
+        return len(self.shape)
+
+    def data_ptr(self):
+        return self._ptr
+
+    def is_contiguous(self):
+        return True
+
+    @classmethod
+    def from_numpy(cls, a):
+        a = np.ascontiguousarray(a)
+        out = cls(a.shape, a.dtype)
+        if a.nbytes:
+            call("docc_b200_h2d", _vp(out._ptr), _vp(a.ctypes.data), a.nbytes)
+        return out
+
+    def to_numpy(self):
+        out = np.empty(self.shape, dtype=self.dtype)
+        if out.nbytes:
+            call("docc_b200_d2h", _vp(out.ctypes.data), _vp(self._ptr), out.nbytes)
+        return out
+
+    def reshape(self, *shape):
+        shape = shape[0] if len(shape) == 1 and isinstance(shape[0], (tuple, list)) else shape
+        shape = list(shape)
+        n = int(np.prod(self.shape, dtype=np.int64)) if self.shape else 1
+        if -1 in shape:
+            known = int(np.prod([v for v in shape if v != -1], dtype=np.int64)) if len(shape) > 1 else 1
+            shape[shape.index(-1)] = n // max(known, 1)
+        if int(np.prod(shape, dtype=np.int64)) != n:
+            raise ValueError("reshape changes the number of elements")
+        view = object.__new__(DeviceArray)
+        view.shape, view.dtype, view.nbytes, view._ptr = tuple(shape), self.dtype, self.nbytes, self._ptr
+        view._owner = self._owner or self  # keeps the allocation alive
+        return view
+
+    def __del__(self):
+        if getattr(self, "_owner", None) is None and getattr(self, "_ptr", None):
+            try:
+                _lib.lib().docc_b200_free(_vp(self._ptr))
+            except Exception:
+                pass
+            self._ptr = None
+
+
 def _is_torch(x) -> bool:
     return type(x).__module__.startswith("torch")
 
@@ -34,7 +99,7 @@ def _prec(x) -> int:
     if _is_torch(x):
         name = str(x.dtype).replace("torch.", "")
     else:
-        name = np.dtype(x.dtype).name
+        name = np.dtype(x.dtype).name  # numpy arrays and DeviceArrays
     try:
         return {"float64": ord("d"), "float32": ord("s"), "float16": ord("h"), "bfloat16": ord("b")}[name]
     except KeyError:
@@ -44,7 +109,7 @@ def _prec(x) -> int:
 def _ptr(x):
     if x is None:
         return _vp(0)
-    if _is_torch(x):
+    if _is_torch(x) or isinstance(x, DeviceArray):
         return _vp(x.data_ptr())
     return _vp(x.ctypes.data)
 
@@ -57,9 +122,9 @@ def _arr(seq):
 def _kind(*xs):
     """Returns (flags, empty_like factory) after checking all arrays live on the same side."""
     xs = [x for x in xs if x is not None]
-    torch_side = [_is_torch(x) for x in xs]
+    torch_side = [_is_torch(x) or isinstance(x, DeviceArray) for x in xs]
     if any(torch_side) and not all(torch_side):
-        raise TypeError("mix of numpy arrays and torch tensors")
+        raise TypeError("mix of host arrays and device tensors")
     if all(torch_side):
         for x in xs:
             if not x.is_cuda:
@@ -74,6 +139,8 @@ def _kind(*xs):
 
 
 def _empty(like, shape, dtype=None):
+    if isinstance(like, DeviceArray):
+        return DeviceArray(shape, dtype or like.dtype)
     if _is_torch(like):
         import torch
 
