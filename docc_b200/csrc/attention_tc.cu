@@ -12,6 +12,8 @@
 //              waits on it) acc = acc * corr_j + O_j from TMEM into registers.
 // QK^T of block j+1 is issued before P_j V_j, so the tensor pipe computes the next scores while the
 // softmax warps work on the current ones. All waits are bounded.
+#include <cstdlib>
+
 #include "attention.h"
 #include "device_math.cuh"
 #include "gemm_tc.h"
@@ -342,6 +344,317 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     }
 }
 
+
+// ---- two query tiles per CTA, P and O resident in tensor memory ------------------------------------------
+// 320 threads: TMA warp, UMMA warp, and one softmax warp group per 128-row query tile. Per tile t the
+// 128 score columns S_t and the 128 output columns O_t live in TMEM (2 x 256 = all 512 columns):
+//   * the softmax group reads S_t, writes P_t (16-bit, two keys per 32-bit column) back over the first
+//     64 columns of S_t with tcgen05.st, and the P V product takes its A operand straight from TMEM;
+//   * O_t is accumulated in place by the tensor pipe (accumulate flag on from the second block). The
+//     running maximum is only raised when it grew by more than 2^8; then the warp rescales its 32 rows
+//     of O_t in TMEM (tcgen05.ld / st) and the row sums. Rows keep exponentials relative to a slightly
+//     stale maximum otherwise, which cancels in the final division by the row sum.
+// The tensor pipe alternates between the tiles: P V of tile t block j, then Q K^T of tile t block
+// j+1 (S_t may only be overwritten once P_t has been consumed), so one group does softmax while the
+// pipe works for the other. K_j / V_j tiles travel through one ring of shared-memory slots and are
+// shared by both tiles.
+template <int D, bool IS_BF16>
+__global__ void __launch_bounds__(320, 1)
+    attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const AttnKernelParams p) {
+    constexpr int DC = D / 64;
+    constexpr uint32_t kTile = uint32_t(DC) * 16384u;
+    constexpr int NS = (227 * 1024 - 2048 - 2 * int(kTile)) / int(kTile) > 8 ? 8 : (227 * 1024 - 2048 - 2 * int(kTile)) / int(kTile);
+    constexpr uint32_t kTmemCols = 512;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sQ = base;                      // two query tiles
+    const uint32_t sKV = sQ + 2 * kTile;           // NS ring slots
+    const uint32_t bars = sKV + uint32_t(NS) * kTile;
+    auto kv_full = [&](int i) { return bars + 8u * uint32_t(i); };
+    auto kv_empty = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
+    auto q_full = [&](int t) { return bars + 128u + 8u * uint32_t(t); };
+    auto s_full = [&](int t) { return bars + 144u + 8u * uint32_t(t); };
+    auto p_full = [&](int t) { return bars + 160u + 8u * uint32_t(t); };
+    auto o_full = [&](int t) { return bars + 176u + 8u * uint32_t(t); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 192u - raw_addr));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_pairs = (p.n_qtiles + 1) / 2;
+    const int pr_raw = blockIdx.x % n_pairs;
+    const int pair = p.causal ? n_pairs - 1 - pr_raw : pr_raw;  // heavier tiles first under a causal mask
+    const int bh = blockIdx.x / n_pairs;
+    const int h = bh % p.H, b = bh / p.H;
+    int q0[2], nb[2];
+    for (int t = 0; t < 2; t++) {
+        q0[t] = (pair * 2 + t) * kBQ;
+        int kv_end = p.Skv;
+        if (p.causal) {
+            const int last = q0[t] + kBQ - 1 + p.causal_off;
+            kv_end = last + 1 < p.Skv ? last + 1 : p.Skv;
+            if (kv_end < 0) kv_end = 0;
+        }
+        nb[t] = q0[t] < p.Sq ? (kv_end + kBKV - 1) / kBKV : 0;
+    }
+    const int n_max = nb[0] > nb[1] ? nb[0] : nb[1];
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < NS; i++) {
+            mbar_init(kv_full(i), 1);
+            mbar_init(kv_empty(i), 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(q_full(t), 1);
+            mbar_init(s_full(t), 1);
+            mbar_init(p_full(t), 4);
+            mbar_init(o_full(t), 1);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && n_max > 0) {
+            for (int t = 0; t < 2; t++) {
+                if (nb[t] == 0) continue;
+                mbar_arrive_expect_tx(q_full(t), kTile);
+                for (int c = 0; c < DC; c++) tma_load_4d(sQ + uint32_t(t) * kTile + uint32_t(c) * 16384u, &tmQ, q_full(t), c * 64, q0[t], h, b);
+            }
+            for (int i = 0; i < 2 * n_max; i++) {  // i = 2j: K_j, i = 2j+1: V_j
+                const int s = i % NS;
+                const uint32_t ph = uint32_t(i / NS) & 1u;
+                if (!mbar_wait(kv_empty(s), ph ^ 1u)) { attn_timeout(p.status, 31); break; }
+                mbar_arrive_expect_tx(kv_full(s), kTile);
+                const CUtensorMap* m = (i & 1) ? &tmV : &tmK;
+                for (int c = 0; c < DC; c++)
+                    tma_load_4d(sKV + uint32_t(s) * kTile + uint32_t(c) * 16384u, m, kv_full(s), c * 64, (i >> 1) * kBKV, h, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0 && n_max > 0) {
+            constexpr uint32_t idesc_qk = make_idesc(kBQ, kBKV, IS_BF16 ? 1 : 0, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc(kBQ, D, IS_BF16 ? 1 : 0, 0, 1);
+            bool ok = true;
+            auto wait_slot = [&](int i) -> uint32_t {  // returns the slot base, 0 on timeout
+                const int s = i % NS;
+                if (!mbar_wait(kv_full(s), uint32_t(i / NS) & 1u)) { attn_timeout(p.status, 32); ok = false; return 0u; }
+                tc_fence_after();
+                return sKV + uint32_t(s) * kTile;
+            };
+            auto issue_qk = [&](int t, uint32_t kb) {
+                const uint32_t d_tmem = tmem_base + uint32_t(t) * 128u;
+                const uint32_t qb = sQ + uint32_t(t) * kTile;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++) {
+                    const uint32_t off = uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u;
+                    umma_f16_ss(d_tmem, make_smem_desc(qb + off, 16u, 1024u), make_smem_desc(kb + off, 16u, 1024u), idesc_qk, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full(t));
+            };
+            for (int t = 0; t < 2 && ok; t++) {
+                if (nb[t] == 0) continue;
+                if (!mbar_wait(q_full(t), 0)) { attn_timeout(p.status, 33); ok = false; }
+            }
+            if (ok) {
+                const uint32_t k0 = wait_slot(0);
+                if (ok) {
+                    for (int t = 0; t < 2; t++) if (nb[t] > 0) issue_qk(t, k0);
+                    umma_commit(kv_empty(0 % NS));
+                }
+            }
+            for (int j = 0; j < n_max && ok; j++) {
+                const uint32_t vb = wait_slot(2 * j + 1);
+                if (!ok) break;
+                uint32_t kb_next = 0;
+                if (j + 1 < n_max) {
+                    kb_next = wait_slot(2 * j + 2);
+                    if (!ok) break;
+                }
+                for (int t = 0; t < 2 && ok; t++) {
+                    if (j >= nb[t]) continue;
+                    if (!mbar_wait(p_full(t), uint32_t(j) & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t o_tmem = tmem_base + 256u + uint32_t(t) * 128u;
+                    const uint32_t p_tmem = tmem_base + uint32_t(t) * 128u;  // P_t over the first 64 columns of S_t
+#pragma unroll
+                    for (int kk = 0; kk < kBKV / 16; kk++) {
+                        const uint64_t db = make_smem_desc(vb + uint32_t(kk) * 2048u, 16384u, 1024u);
+                        umma_f16_ts(o_tmem, p_tmem + uint32_t(kk) * 8u, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(o_full(t));
+                    if (j + 1 < nb[t]) issue_qk(t, kb_next);
+                }
+                if (!ok) break;
+                umma_commit(kv_empty((2 * j + 1) % NS));
+                if (j + 1 < n_max) umma_commit(kv_empty((2 * j + 2) % NS));
+            }
+        }
+    } else {
+        // ---------------- softmax groups ----------------
+        const int t = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const int row = q0[t] + r;
+        const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
+        const uint32_t s_addr = lane_addr + uint32_t(t) * 128u;
+        const uint32_t o_addr = lane_addr + 256u + uint32_t(t) * 128u;
+        const int n_t = nb[t];
+        float m = -INFINITY;  // maximum the stored exponentials are relative to
+        float l = 0.f;
+        bool ok = true;
+        const int row_limit = p.causal ? row + p.causal_off : p.Skv - 1;
+
+        for (int j = 0; j < n_t && ok; j++) {
+            const int k0 = j * kBKV;
+            if (!mbar_wait(s_full(t), uint32_t(j) & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 35);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const bool need_mask = (k0 + kBKV > p.Skv) || (p.causal && k0 + kBKV - 1 > q0[t] + p.causal_off);
+            const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;
+            float bm = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kBKV / 32; c++) {
+                uint32_t sv[32];
+                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i <= visible) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                }
+            }
+            const float m_cand = fmaxf(m, bm * p.scale_log2);
+            // raise the reference maximum only when it moved by more than 8 (a factor 256 of headroom)
+            const bool raise = m_cand > m + 8.0f;  // also true on the first block (m = -inf) when any key is visible
+            if (__any_sync(0xffffffffu, raise)) {
+                const float m_new = raise ? m_cand : m;
+                const float f = raise ? ex2(m - m_new) : 1.0f;  // 0 when m = -inf
+                if (j > 0) {
+                    // S_t of this block is complete, hence the previous P V has finished: O_t is quiescent
+#pragma unroll
+                    for (int c = 0; c < D / 32; c++) {
+                        uint32_t o[32];
+                        tmem_ld_x32(o_addr + uint32_t(c) * 32u, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st_x32(o_addr + uint32_t(c) * 32u, o);
+                    }
+                    tmem_st_wait();
+                }
+                l *= f;
+                m = m_new;
+            }
+            const float m_ref = (m == -INFINITY) ? 0.f : m;
+            float bl = 0.f;
+#pragma unroll
+            for (int c = 0; c < kBKV / 32; c++) {
+                uint32_t sv[32];
+                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float x0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_ref));
+                    float x1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref));
+                    if (need_mask) {
+                        if (c * 32 + 2 * i > visible) x0 = 0.f;
+                        if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
+                    }
+                    bl += x0 + x1;
+                    pk[i] = pack2<IS_BF16>(x0, x1);
+                }
+                // keys 32c..32c+31 -> columns 16c..16c+15 of S_t (already consumed: they held keys < 32(c/2+1))
+                tmem_st_x16(s_addr + uint32_t(c) * 16u, pk);
+            }
+            l += bl;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(t));
+        }
+
+        if (n_t > 0 && ok) {
+            if (!mbar_wait(o_full(t), uint32_t(n_t - 1) & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 36);
+                ok = false;
+            }
+            tc_fence_after();
+        }
+        using T = typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* optr = static_cast<T*>(p.O) + b * p.os_b + h * p.os_h + (long long)row * p.os_s;
+        if (q0[t] < p.Sq) {
+#pragma unroll
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t o[32];
+                if (n_t > 0 && ok) {
+                    tmem_ld_x32(o_addr + uint32_t(c) * 32u, o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = 0u;
+                }
+                if (row < p.Sq) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        uint4 w;
+                        w.x = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+                        w.y = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+                        w.z = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+                        w.w = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = w;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+bool g_attr2_done[16][4] = {};
+
+template <int D, bool IS_BF16>
+int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+            const AttnKernelParams& kp, int slot) {
+    constexpr int kTileBytes = (D / 64) * 16384;
+    constexpr int NS = (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes > 8 ? 8 : (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes;
+    constexpr size_t smem = size_t(kTileBytes) * (2 + NS) + 1024 + 256;
+    auto kern = attention_tc2_kernel<D, IS_BF16>;
+    if (!g_attr2_done[ctx->device & 15][slot]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        g_attr2_done[ctx->device & 15][slot] = true;
+    }
+    const int64_t grid = p.B * p.H * ((kp.n_qtiles + 1) / 2);
+    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(tq, tk, tv, kp);
+    return after_launch(ctx, "attention_tc2_kernel");
+}
+
 bool g_attr_done[16][4] = {};
 
 template <int D, bool IS_BF16>
@@ -395,6 +708,11 @@ int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, c
     kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
     kp.status = ctx->status_dev;
     const bool bf = p.prec == DOCC_B200_PREC_B;
+    static const bool single_tile = [] { const char* e = getenv("DOCC_B200_ATTENTION_SINGLE_TILE"); return e && e[0] == '1'; }();
+    if (!single_tile && p.Sq > kBQ) {
+        if (p.D == 128) return bf ? launch2<128, true>(ctx, p, tq, tk, tv, kp, 0) : launch2<128, false>(ctx, p, tq, tk, tv, kp, 1);
+        return bf ? launch2<64, true>(ctx, p, tq, tk, tv, kp, 2) : launch2<64, false>(ctx, p, tq, tk, tv, kp, 3);
+    }
     if (p.D == 128) return bf ? launch<128, true>(ctx, p, tq, tk, tv, kp, 0) : launch<128, false>(ctx, p, tq, tk, tv, kp, 1);
     return bf ? launch<64, true>(ctx, p, tq, tk, tv, kp, 2) : launch<64, false>(ctx, p, tq, tk, tv, kp, 3);
 }
