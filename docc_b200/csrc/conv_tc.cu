@@ -36,6 +36,7 @@ struct ConvKernelParams {
     int r_max;         // output rows per tile (r_max * Wo <= 256)
     int tiles_m;
     long long total_units;  // tiles_m * N * Ho output-row units
+    int tma_out;  // Y rows are 16-byte aligned: full 32-pixel groups go out through TMA stores
     const float* bias;
     float* Y;
     DeviceStatus* status;
@@ -76,13 +77,14 @@ __device__ __forceinline__ bool next_tile(const ConvKernelParams& p, long long& 
 __global__ void __launch_bounds__(kThreads, 1)
     conv_tc_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
                    const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmX1,
-                   const ConvKernelParams p) {
+                   const __grid_constant__ CUtensorMap tmY, const ConvKernelParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     const uint32_t sA = base;
     const uint32_t sB = sA + kStages * kABytes;
-    const uint32_t bars = sB + kStages * kBBytes;
+    const uint32_t sStage = sB + kStages * kBBytes;  // four 4 KB staging tiles (one per epilogue warp)
+    const uint32_t bars = sStage + 4 * 4096u;
     auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
     auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
     auto tfull_bar = [&](int i) { return bars + 128u + 8u * uint32_t(i); };
@@ -215,7 +217,40 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float bv = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.f;
             float* yrow = p.Y + ((long long)t.n * p.c_out + (row_ok ? oc : 0)) * plane + (long long)t.oh0 * p.Wo;
             const bool vec = (reinterpret_cast<uintptr_t>(yrow) & 15) == 0;
-            for (int c = 0; c < ncols; c += 16) {
+            const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
+            const int pix0 = t.oh0 * p.Wo;
+            int c = 0;
+            if (p.tma_out) {
+                // whole 32-pixel groups leave through a swizzled staging tile and one TMA store per warp:
+                // 32 channels x 32 pixels, every row a full 128-byte line of Y
+                for (; c + 32 <= ncols; c += 32) {
+                    if (lane == 0) tma_store_wait_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (int sub = 0; sub < 2; sub++) {
+                        uint32_t r[16];
+                        tmem_ld_x16(t_addr + uint32_t(c + sub * 16), r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; v4++) {
+                            const int chunk = sub * 4 + v4;
+                            const uint32_t dst = stage_base + uint32_t(lane) * 128u + uint32_t((chunk ^ (lane & 7)) * 16);
+                            const uint32_t w0 = __float_as_uint(__uint_as_float(r[v4 * 4 + 0]) + bv);
+                            const uint32_t w1 = __float_as_uint(__uint_as_float(r[v4 * 4 + 1]) + bv);
+                            const uint32_t w2 = __float_as_uint(__uint_as_float(r[v4 * 4 + 2]) + bv);
+                            const uint32_t w3 = __float_as_uint(__uint_as_float(r[v4 * 4 + 3]) + bv);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && t.m0 + q * 32 < p.c_out) {
+                        tma_store_3d(&tmY, stage_base, pix0 + c, t.m0 + q * 32, t.n);  // channels >= C_out are clipped
+                        tma_store_commit();
+                    }
+                }
+            }
+            for (; c < ncols; c += 16) {
                 uint32_t r[16];
                 tmem_ld_x16(t_addr + uint32_t(c), r);
                 tmem_ld_wait();
@@ -240,6 +275,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(int(buf)));
         }
+        if (p.tma_out && lane == 0) tma_store_wait<0>();
     }
 
     tc_fence_before();
@@ -253,31 +289,48 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---- layout pre-passes ---------------------------------------------------------------------------
 template <typename TIn> __device__ __forceinline__ float ld_f(const TIn* p) { return to_float(*p); }
 
-// X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16. 32x32 tiles through shared memory.
+// X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16. A block moves 64 pixels x 64 channels through shared
+// memory as 32-bit words holding a channel pair: reads walk pixels (coalesced in NCHW), writes walk
+// channels, so every pixel's 64 channels leave as one full 128-byte line. Requires C % 64 == 0.
 template <typename TIn, bool SPLIT>
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ X, __nv_bfloat16* __restrict__ hi,
                                                            __nv_bfloat16* __restrict__ lo, int C, long long HW) {
-    __shared__ float tile[32][33];
+    __shared__ uint32_t tile_hi[64][33];
+    __shared__ uint32_t tile_lo[SPLIT ? 64 : 1][33];
     const long long n = blockIdx.z;
-    const long long p0 = (long long)blockIdx.x * 32;
-    const int c0 = blockIdx.y * 32;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const TIn* xin = X + n * C * HW;
-    for (int j = ty; j < 32; j += 8) {
-        const int c = c0 + j;
-        const long long px = p0 + tx;
-        tile[j][tx] = (c < C && px < HW) ? ld_f(xin + c * HW + px) : 0.f;
+    const long long p0 = (long long)blockIdx.x * 64;
+    const int c0 = blockIdx.y * 64;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;  // 8 warps
+    const TIn* xin = X + (n * C + c0) * HW;
+    // warp w, iteration i: channel pair cp = w + 8*(i/2), pixel half (i&1)
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int cp = w + 8 * (i >> 1);
+        const int px = (i & 1) * 32 + lane;
+        const long long gp = p0 + px;
+        float a = 0.f, b = 0.f;
+        if (gp < HW) {
+            a = ld_f(xin + (long long)(2 * cp) * HW + gp);
+            b = ld_f(xin + (long long)(2 * cp + 1) * HW + gp);
+        }
+        const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+        tile_hi[px][cp] = uint32_t(__bfloat16_as_ushort(ah)) | (uint32_t(__bfloat16_as_ushort(bh)) << 16);
+        if (SPLIT) {
+            const __nv_bfloat16 al = __float2bfloat16_rn(a - __bfloat162float(ah)), bl = __float2bfloat16_rn(b - __bfloat162float(bh));
+            tile_lo[px][cp] = uint32_t(__bfloat16_as_ushort(al)) | (uint32_t(__bfloat16_as_ushort(bl)) << 16);
+        }
     }
     __syncthreads();
-    for (int j = ty; j < 32; j += 8) {
-        const long long px = p0 + j;
-        const int c = c0 + tx;
-        if (px < HW && c < C) {
-            const float v = tile[tx][j];
-            const __nv_bfloat16 h = __float2bfloat16_rn(v);
-            const long long o = (n * HW + px) * C + c;
-            hi[o] = h;
-            if (SPLIT) lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
+    uint32_t* out_hi = reinterpret_cast<uint32_t*>(hi);
+    uint32_t* out_lo = reinterpret_cast<uint32_t*>(lo);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int px = w + 8 * i;
+        const long long gp = p0 + px;
+        if (gp < HW) {
+            const long long o = ((n * HW + gp) * C + c0) / 2 + lane;
+            out_hi[o] = tile_hi[px][lane];
+            if (SPLIT) out_lo[o] = tile_lo[px][lane];
         }
     }
 }
@@ -320,7 +373,7 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     __nv_bfloat16* w_lo = w_hi + (w_elems + 63) / 64 * 64;
 
     {
-        dim3 grid(unsigned(ceil_div(HW, 32)), unsigned(ceil_div(q.C, 32)), unsigned(q.N));
+        dim3 grid(unsigned(ceil_div(HW, 64)), unsigned(q.C / 64), unsigned(q.N));
         if (grid.z > 65535) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: batch too large");
         if (split) nchw_to_nhwc_kernel<float, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW);
         else nchw_to_nhwc_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW);
@@ -332,8 +385,15 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
         DOCC_TRY(after_launch(ctx, "weight_relayout_kernel"));
     }
 
-    CUtensorMap maps[4];
+    CUtensorMap maps[5];
     memset(maps, 0, sizeof(maps));
+    const bool tma_out = q.Wo % 4 == 0 && reinterpret_cast<uintptr_t>(Y) % 16 == 0;
+    if (tma_out) {
+        const uint64_t yd[3] = {uint64_t(q.Ho * q.Wo), uint64_t(q.c_out), uint64_t(q.N)};
+        const uint64_t ys[2] = {uint64_t(q.Ho * q.Wo) * 4, uint64_t(q.Ho * q.Wo) * q.c_out * 4};
+        const uint32_t yb[3] = {32, 32, 1};
+        DOCC_TRY(encode_tmap(&maps[4], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, CU_TENSOR_MAP_SWIZZLE_128B, Y, 3, yd, ys, yb));
+    }
     for (int i = 0; i < 2; i++) {
         const __nv_bfloat16* wp = (i == 1 && split) ? w_lo : w_hi;
         const __nv_bfloat16* xp = (i == 1 && split) ? x_lo : x_hi;
@@ -363,9 +423,10 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     if (p.r_max > 8) p.r_max = 8;
     p.tiles_m = int(ceil_div(q.c_out, 128));
     p.total_units = (long long)p.tiles_m * q.N * q.Ho;
+    p.tma_out = tma_out ? 1 : 0;
     p.bias = bias; p.Y = Y; p.status = ctx->status_dev;
 
-    const size_t smem = size_t(kStages) * (kABytes + kBBytes) + 1024 + 256;
+    const size_t smem = size_t(kStages) * (kABytes + kBBytes) + 4 * 4096 + 1024 + 256;
     if (!g_conv_attr[ctx->device & 15]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         g_conv_attr[ctx->device & 15] = true;
@@ -373,7 +434,7 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     // enough CTAs that each gets at least one full tile; never more than one per SM
     long long grid = ceil_div(p.total_units, p.r_max);
     if (grid > ctx->sm_count) grid = ctx->sm_count;
-    conv_tc_kernel<<<unsigned(grid), kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    conv_tc_kernel<<<unsigned(grid), kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
     return after_launch(ctx, "conv_tc_kernel");
 }
 

@@ -34,6 +34,7 @@ constexpr int kThreads = 320;  // TMA warp, UMMA warp, eight epilogue warps
 constexpr int kMaxStages = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kSmemBudget = 227 * 1024;
+constexpr uint32_t kStagingBytes = 8 * 4096;
 
 struct TcKernelParams {
     int M, N, K, batch;
@@ -58,7 +59,8 @@ struct TcKernelParams {
     void* out;
     long long ldo, out_bs;
     int out_prec;
-    int vec_out, vec_res;
+    int vec_out, vec_res, vec_bias;
+    int tma_out;  // epilogue goes through swizzled staging tiles and TMA stores
     DeviceStatus* status;
 };
 
@@ -71,17 +73,19 @@ __device__ __forceinline__ void report_timeout(DeviceStatus* st, unsigned where)
     __threadfence_system();
 }
 
+// Epilogue arithmetic for 16 consecutive columns of one accumulator row:
+// v = act(alpha*acc + beta*C + bias) + residual. Columns at or beyond N are left untouched.
 template <typename OutT>
-__device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const uint32_t (&r)[16], long long row, int col0, int b) {
-    const int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
-    if (ncols <= 0) return;
-    float v[16];
+__device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const uint32_t (&r)[16], long long row, int col0, int b,
+                                                bool row_ok, float (&v)[16]) {
+    int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
+    if (ncols < 0 || !row_ok) ncols = 0;
 #pragma unroll
     for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]) * p.alpha;
-    OutT* orow = static_cast<OutT*>(p.out) + b * p.out_bs + row * p.ldo + col0;
     constexpr int EPV = 16 / sizeof(OutT);  // elements per 16-byte vector
     const bool full = ncols == 16;
-    if (p.beta != 0.f) {
+    if (p.beta != 0.f && ncols > 0) {
+        const OutT* orow = static_cast<const OutT*>(p.out) + b * p.out_bs + row * p.ldo + col0;
         if (full && p.vec_out) {
 #pragma unroll
             for (int q = 0; q < 16 / EPV; q++) {
@@ -93,20 +97,28 @@ __device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const ui
             for (int j = 0; j < ncols; j++) v[j] += p.beta * to_float(orow[j]);
         }
     }
-    if (p.bias_mode == 1) {
+    if (p.bias_mode == 1 && ncols > 0) {
+        if (full && p.vec_bias) {
 #pragma unroll
-        for (int j = 0; j < 16; j++)
-            if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
-    } else if (p.bias_mode == 2) {
+            for (int q = 0; q < 4; q++) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(p.bias + col0) + q);
+                v[q * 4 + 0] += bv.x; v[q * 4 + 1] += bv.y; v[q * 4 + 2] += bv.z; v[q * 4 + 3] += bv.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < ncols) v[j] += __ldg(p.bias + col0 + j);
+        }
+    } else if (p.bias_mode == 2 && row_ok) {
         const float bv = __ldg(p.bias + row);
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] += bv;
     }
     if (p.act != DOCC_B200_ACT_NONE) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = apply_act(p.act, v[j]);
+        for (int j = 0; j < 16; j++) v[j] = apply_act_fast(p.act, v[j]);
     }
-    if (p.residual) {
+    if (p.residual && ncols > 0) {
         const OutT* rrow = static_cast<const OutT*>(p.residual) + b * p.res_bs + row * p.ldr + col0;
         if (full && p.vec_res) {
 #pragma unroll
@@ -119,7 +131,16 @@ __device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const ui
             for (int j = 0; j < ncols; j++) v[j] += to_float(rrow[j]);
         }
     }
-    if (full && p.vec_out) {
+}
+
+// Direct store of 16 columns (used when the output is not 16-byte aligned for TMA).
+template <typename OutT>
+__device__ __forceinline__ void epilogue_store_direct(const TcKernelParams& p, const float (&v)[16], long long row, int col0, int b) {
+    const int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
+    if (ncols <= 0) return;
+    OutT* orow = static_cast<OutT*>(p.out) + b * p.out_bs + row * p.ldo + col0;
+    constexpr int EPV = 16 / sizeof(OutT);
+    if (ncols == 16 && p.vec_out) {
 #pragma unroll
         for (int q = 0; q < 16 / EPV; q++) {
             Pack<OutT, EPV> o;
@@ -129,6 +150,64 @@ __device__ __forceinline__ void epilogue_chunk(const TcKernelParams& p, const ui
         }
     } else {
         for (int j = 0; j < ncols; j++) orow[j] = from_float<OutT>(v[j]);
+    }
+}
+
+// 16 columns of this lane's row into the warp's staging tile: 32 rows x 128 bytes, 128-byte swizzle
+// (16-byte chunk c of row r sits at chunk c ^ (r & 7)), the layout a SWIZZLE_128B TMA store reads.
+// `sub` is the index of the 16-column group inside the 128-byte row.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_stage(uint32_t stage_base, int lane, int sub, const float (&v)[16]) {
+    constexpr int EPV = 16 / sizeof(OutT);
+    constexpr int CHUNKS = 16 / EPV;  // 16-byte chunks per 16 columns: 4 (fp32) or 2 (16-bit)
+#pragma unroll
+    for (int q = 0; q < CHUNKS; q++) {
+        Pack<OutT, EPV> o;
+#pragma unroll
+        for (int e = 0; e < EPV; e++) o.v[e] = from_float<OutT>(v[q * EPV + e]);
+        const uint4 w = *reinterpret_cast<const uint4*>(&o);
+        const int chunk = sub * CHUNKS + q;
+        const uint32_t dst = stage_base + uint32_t(lane) * 128u + uint32_t((chunk ^ (lane & 7)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
+    }
+}
+
+template <typename OutT>
+__device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUtensorMap* tm_out, uint32_t stage_base, uint32_t t_addr,
+                                              int c_begin, int c_end, long long row, int row0, int n0, int b, int lane) {
+    const bool row_ok = row < p.M;
+    if (p.tma_out) {
+        constexpr int BOX = 128 / sizeof(OutT);  // columns per 128-byte staging row
+        for (int c0 = c_begin; c0 < c_end; c0 += BOX) {
+            // the previous TMA store must have finished reading the staging tile
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int sub = 0; sub < BOX / 16; sub++) {
+                uint32_t r[16];
+                tmem_ld_x16(t_addr + uint32_t(c0 + sub * 16), r);
+                tmem_ld_wait();
+                float v[16];
+                epilogue_values<OutT>(p, r, row, n0 + c0 + sub * 16, b, row_ok, v);
+                epilogue_stage<OutT>(stage_base, lane, sub, v);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            // rows >= M and columns >= N are clipped by the tensor map
+            if (lane == 0 && n0 + c0 < p.N && row0 < p.M) {
+                tma_store_3d(tm_out, stage_base, n0 + c0, row0, b);
+                tma_store_commit();
+            }
+        }
+    } else {
+        for (int c = c_begin; c < c_end; c += 16) {
+            uint32_t r[16];
+            tmem_ld_x16(t_addr + uint32_t(c), r);
+            tmem_ld_wait();
+            float v[16];
+            epilogue_values<OutT>(p, r, row, n0 + c, b, row_ok, v);
+            if (row_ok) epilogue_store_direct<OutT>(p, v, row, n0 + c, b);
+        }
     }
 }
 
@@ -151,13 +230,14 @@ __device__ __forceinline__ void tile_coords(const TcKernelParams& p, int t, int&
 __global__ void __launch_bounds__(kThreads, 1)
     tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
                    const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
-                   const TcKernelParams p) {
+                   const __grid_constant__ CUtensorMap tmOut, const TcKernelParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     const uint32_t sA = base;
     const uint32_t sB = sA + uint32_t(p.stages) * p.a_bytes;
-    const uint32_t bars = sB + uint32_t(p.stages) * p.b_bytes;
+    const uint32_t sStage = sB + uint32_t(p.stages) * p.b_bytes;  // eight 4 KB staging tiles for the TMA-store epilogue
+    const uint32_t bars = sStage + kStagingBytes;
     auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
     auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
     auto tfull_bar = [&](int i) { return bars + 128u + 8u * uint32_t(i); };
@@ -313,26 +393,23 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after();
-            const long long row = m0 + (tall ? wg * 128 : 0) + q * 32 + lane;
+            const int row0 = m0 + (tall ? wg * 128 : 0) + q * 32;
+            const long long row = row0 + lane;
             const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + region * 256u;
             // tall tiles: each group drains its own 128 rows; otherwise the groups split the columns
-            const int half_cols = ((p.bn / 2) + 15) / 16 * 16;
+            // (at a multiple of 64 so that both halves are whole staging rows for every output type)
+            const int half_cols = ((p.bn / 2) + 63) / 64 * 64;
             const int c_begin = tall ? 0 : (wg == 0 ? 0 : half_cols);
-            const int c_end = tall ? p.bn : (wg == 0 ? half_cols : p.bn);
-            for (int c = c_begin; c < c_end; c += 16) {
-                uint32_t r[16];
-                tmem_ld_x16(t_addr + uint32_t(c), r);
-                tmem_ld_wait();
-                if (row < p.M) {
-                    if (p.out_prec == DOCC_B200_PREC_S) epilogue_chunk<float>(p, r, row, n0 + c, b);
-                    else if (p.out_prec == DOCC_B200_PREC_B) epilogue_chunk<__nv_bfloat16>(p, r, row, n0 + c, b);
-                    else epilogue_chunk<__half>(p, r, row, n0 + c, b);
-                }
-            }
+            const int c_end = tall ? p.bn : (wg == 0 ? (half_cols < p.bn ? half_cols : p.bn) : p.bn);
+            const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
+            if (p.out_prec == DOCC_B200_PREC_S) epilogue_tile<float>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
+            else if (p.out_prec == DOCC_B200_PREC_B) epilogue_tile<__nv_bfloat16>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
+            else epilogue_tile<__half>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(int(region)));
         }
+        if (p.tma_out && lane == 0) tma_store_wait<0>();  // staging tiles must outlive the bulk stores that read them
     }
 
     tc_fence_before();
@@ -551,7 +628,7 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
     p.group_m = bm == 256 ? 12 : 16;
     p.num_kb = int(ceil_div(K, kBK));
     p.b_bytes = uint32_t((bn * 128 + 1023) / 1024 * 1024);
-    int stages = (kSmemBudget - 2048) / int(p.a_bytes + p.b_bytes);
+    int stages = (kSmemBudget - 2048 - int(kStagingBytes)) / int(p.a_bytes + p.b_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     const int64_t k_iters = int64_t(p.num_kb) * npass;
     if (stages > k_iters && k_iters >= 2) stages = int(k_iters);
@@ -572,10 +649,24 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
                  ep.residual_batch_stride % epv == 0)
                     ? 1
                     : 0;
+    p.vec_bias = (ep.bias && reinterpret_cast<uintptr_t>(ep.bias) % 16 == 0) ? 1 : 0;
+    p.tma_out = p.vec_out;
     p.status = ctx->status_dev;
 
-    CUtensorMap maps[4];
+    CUtensorMap maps[5];
     memset(maps, 0, sizeof(maps));
+    if (p.tma_out) {
+        // output as [batch][M][N] with 32-row x 128-byte boxes; the map clips the M and N tails
+        const uint64_t od[3] = {uint64_t(N), uint64_t(M), uint64_t(batch)};
+        uint64_t obs = uint64_t(ep.out_batch_stride) * oes;
+        if (batch == 1 || obs == 0) obs = uint64_t(ep.ldo) * oes * uint64_t(M);
+        const uint64_t os[2] = {uint64_t(ep.ldo) * oes, obs};
+        const uint32_t ob[3] = {uint32_t(128 / oes), 32, 1};
+        const CUtensorMapDataType odt = ep.out_prec == DOCC_B200_PREC_S ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                        : ep.out_prec == DOCC_B200_PREC_B ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        DOCC_TRY(encode_tmap(&maps[4], odt, oes, CU_TENSOR_MAP_SWIZZLE_128B, ep.out, 3, od, os, ob));
+    }
     auto encode_operand = [&](CUtensorMap* m, const TcOperand& o, int64_t mn, uint32_t mn_box, bool bcast) -> int {
         const uint64_t nb = bcast ? 1 : uint64_t(batch);
         uint64_t bs_bytes = uint64_t(o.batch_stride) * 2;
@@ -596,14 +687,14 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         DOCC_TRY(encode_operand(&maps[2 + i], B[i < n_b ? i : 0], N, uint32_t(bn), p.b_bcast || batch == 1));
     }
 
-    const size_t smem = size_t(stages) * (p.a_bytes + p.b_bytes) + 1024 + 256;
+    const size_t smem = size_t(stages) * (p.a_bytes + p.b_bytes) + kStagingBytes + 1024 + 256;
     if (!g_attr_set[ctx->device & 15]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
         g_attr_set[ctx->device & 15] = true;
     }
     const int64_t total_tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
     const int grid = int(total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count);
-    tc_gemm_kernel<<<grid, kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+    tc_gemm_kernel<<<grid, kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
     return after_launch(ctx, "tc_gemm_kernel");
 }
 
