@@ -67,7 +67,8 @@ __device__ __forceinline__ float apply_act(int act, float x) {
 // critical path of the accumulator drain.
 __device__ __forceinline__ float erf_fast(float x) {
     const float ax = fabsf(x);
-    const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, ax, 1.0f)));
     float poly = fmaf(t, 1.061405429f, -1.453152027f);
     poly = fmaf(t, poly, 1.421413741f);
     poly = fmaf(t, poly, -0.284496736f);

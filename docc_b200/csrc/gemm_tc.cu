@@ -75,7 +75,8 @@ __device__ __forceinline__ void report_timeout(DeviceStatus* st, unsigned where)
 
 // Epilogue arithmetic for 16 consecutive columns of one accumulator row:
 // v = act(alpha*acc + beta*C + bias) + residual. Columns at or beyond N are left untouched.
-template <typename OutT>
+// ACT is the activation code, or -1 to select it at run time (rare codes only).
+template <typename OutT, int ACT>
 __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const uint32_t (&r)[16], long long row, int col0, int b,
                                                 bool row_ok, float (&v)[16]) {
     int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
@@ -94,7 +95,9 @@ __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const u
                 for (int e = 0; e < EPV; e++) v[q * EPV + e] += p.beta * to_float(c.v[e]);
             }
         } else {
-            for (int j = 0; j < ncols; j++) v[j] += p.beta * to_float(orow[j]);
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < ncols) v[j] += p.beta * to_float(orow[j]);
         }
     }
     if (p.bias_mode == 1 && ncols > 0) {
@@ -114,7 +117,13 @@ __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const u
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] += bv;
     }
-    if (p.act != DOCC_B200_ACT_NONE) {
+    if constexpr (ACT == DOCC_B200_ACT_GELU_ERF) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = 0.5f * v[j] * (1.0f + erf_fast(v[j] * 0.70710678118654752440f));
+    } else if constexpr (ACT == DOCC_B200_ACT_RELU) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = fmaxf(v[j], 0.f);
+    } else if constexpr (ACT == -1) {
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] = apply_act_fast(p.act, v[j]);
     }
@@ -128,7 +137,9 @@ __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const u
                 for (int e = 0; e < EPV; e++) v[q * EPV + e] += to_float(c.v[e]);
             }
         } else {
-            for (int j = 0; j < ncols; j++) v[j] += to_float(rrow[j]);
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (j < ncols) v[j] += to_float(rrow[j]);
         }
     }
 }
@@ -149,7 +160,9 @@ __device__ __forceinline__ void epilogue_store_direct(const TcKernelParams& p, c
             *reinterpret_cast<Pack<OutT, EPV>*>(orow + q * EPV) = o;
         }
     } else {
-        for (int j = 0; j < ncols; j++) orow[j] = from_float<OutT>(v[j]);
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+            if (j < ncols) orow[j] = from_float<OutT>(v[j]);
     }
 }
 
@@ -172,7 +185,7 @@ __device__ __forceinline__ void epilogue_stage(uint32_t stage_base, int lane, in
     }
 }
 
-template <typename OutT>
+template <typename OutT, int ACT>
 __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUtensorMap* tm_out, uint32_t stage_base, uint32_t t_addr,
                                               int c_begin, int c_end, long long row, int row0, int n0, int b, int lane) {
     const bool row_ok = row < p.M;
@@ -188,7 +201,7 @@ __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUt
                 tmem_ld_x16(t_addr + uint32_t(c0 + sub * 16), r);
                 tmem_ld_wait();
                 float v[16];
-                epilogue_values<OutT>(p, r, row, n0 + c0 + sub * 16, b, row_ok, v);
+                epilogue_values<OutT, ACT>(p, r, row, n0 + c0 + sub * 16, b, row_ok, v);
                 epilogue_stage<OutT>(stage_base, lane, sub, v);
             }
             fence_proxy_async_smem();
@@ -205,7 +218,7 @@ __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUt
             tmem_ld_x16(t_addr + uint32_t(c), r);
             tmem_ld_wait();
             float v[16];
-            epilogue_values<OutT>(p, r, row, n0 + c, b, row_ok, v);
+            epilogue_values<OutT, ACT>(p, r, row, n0 + c, b, row_ok, v);
             if (row_ok) epilogue_store_direct<OutT>(p, v, row, n0 + c, b);
         }
     }
@@ -402,9 +415,19 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int c_begin = tall ? 0 : (wg == 0 ? 0 : half_cols);
             const int c_end = tall ? p.bn : (wg == 0 ? (half_cols < p.bn ? half_cols : p.bn) : p.bn);
             const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
-            if (p.out_prec == DOCC_B200_PREC_S) epilogue_tile<float>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
-            else if (p.out_prec == DOCC_B200_PREC_B) epilogue_tile<__nv_bfloat16>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
-            else epilogue_tile<__half>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane);
+#define DOCC_EPI(T, A) epilogue_tile<T, A>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane)
+#define DOCC_EPI_ACT(T)                                                  \
+    do {                                                                 \
+        if (p.act == DOCC_B200_ACT_NONE) DOCC_EPI(T, 0);                 \
+        else if (p.act == DOCC_B200_ACT_GELU_ERF) DOCC_EPI(T, 1);        \
+        else if (p.act == DOCC_B200_ACT_RELU) DOCC_EPI(T, 2);            \
+        else DOCC_EPI(T, -1);                                            \
+    } while (0)
+            if (p.out_prec == DOCC_B200_PREC_S) DOCC_EPI_ACT(float);
+            else if (p.out_prec == DOCC_B200_PREC_B) DOCC_EPI_ACT(__nv_bfloat16);
+            else DOCC_EPI_ACT(__half);
+#undef DOCC_EPI_ACT
+#undef DOCC_EPI
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(int(region)));
