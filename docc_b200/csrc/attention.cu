@@ -94,6 +94,10 @@ int attention_device(Ctx* ctx, const AttnProblem& p, const void* Q, const void* 
         int s = attention_tc(ctx, p, Q, K, V, O);
         if (s != DOCC_B200_ERR_UNSUPPORTED) return s;
     }
+    if (p.prec == DOCC_B200_PREC_S && !(flags & DOCC_B200_FLAG_FP32_EXACT)) {
+        int s = attention_tc_f32(ctx, p, Q, K, V, O);
+        if (s != DOCC_B200_ERR_UNSUPPORTED) return s;
+    }
     switch (p.prec) {
         case DOCC_B200_PREC_S: return launch_rows<float>(ctx, p, Q, K, V, O);
         case DOCC_B200_PREC_B: return launch_rows<__nv_bfloat16>(ctx, p, Q, K, V, O);

@@ -17,4 +17,7 @@ struct AttnProblem {
 // Returns DOCC_B200_ERR_UNSUPPORTED for shapes the tensor-core kernel does not tile.
 int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O);
 
+// fp32 inputs and output, head_dim 64: split-bf16 tensor-core path (three products per contraction).
+int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O);
+
 }  // namespace docc_b200

@@ -345,6 +345,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 }
 
 
+__host__ __device__ constexpr int attn2_slots(int d, bool split) {
+    const int tile = (d / 64) * 16384;
+    const int n = (227 * 1024 - 2048 - 2 * (split ? 2 : 1) * tile) / tile;
+    return n > 8 ? 8 : n;
+}
+
 // ---- two query tiles per CTA, P and O resident in tensor memory ------------------------------------------
 // 320 threads: TMA warp, UMMA warp, and one softmax warp group per 128-row query tile. Per tile t the
 // 128 score columns S_t and the 128 output columns O_t live in TMEM (2 x 256 = all 512 columns):
@@ -358,19 +364,26 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 // j+1 (S_t may only be overwritten once P_t has been consumed), so one group does softmax while the
 // pipe works for the other. K_j / V_j tiles travel through one ring of shared-memory slots and are
 // shared by both tiles.
-template <int D, bool IS_BF16>
+// SPLIT: fp32 attention. Q, K, V arrive as bf16 hi/lo planes (x = hi + lo to ~16 bits); Q K^T and
+// P V each run three products (lo*hi, hi*lo, hi*hi) into the same accumulator, P is split the same way
+// (P_hi in columns 0-63 and P_lo in columns 64-127 of S_t), and O leaves as fp32.
+template <int D, bool IS_BF16, bool SPLIT>
 __global__ void __launch_bounds__(320, 1)
     attention_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmV, const AttnKernelParams p) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQl,
+                         const __grid_constant__ CUtensorMap tmKl, const __grid_constant__ CUtensorMap tmVl,
+                         const AttnKernelParams p) {
     constexpr int DC = D / 64;
     constexpr uint32_t kTile = uint32_t(DC) * 16384u;
-    constexpr int NS = (227 * 1024 - 2048 - 2 * int(kTile)) / int(kTile) > 8 ? 8 : (227 * 1024 - 2048 - 2 * int(kTile)) / int(kTile);
+    constexpr int QP = SPLIT ? 2 : 1;  // planes per query tile
+    constexpr int EB = SPLIT ? 4 : 2;  // ring entries per key block: K_hi, [K_lo], V_hi, [V_lo]
+    constexpr int NS = attn2_slots(D, SPLIT);
     constexpr uint32_t kTmemCols = 512;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
-    const uint32_t sQ = base;                      // two query tiles
-    const uint32_t sKV = sQ + 2 * kTile;           // NS ring slots
+    const uint32_t sQ = base;                      // two query tiles (x hi/lo planes): tile t plane pl at (t*QP + pl)*kTile
+    const uint32_t sKV = sQ + 2 * QP * kTile;      // NS ring slots
     const uint32_t bars = sKV + uint32_t(NS) * kTile;
     auto kv_full = [&](int i) { return bars + 8u * uint32_t(i); };
     auto kv_empty = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
@@ -429,17 +442,20 @@ __global__ void __launch_bounds__(320, 1)
         if (lane == 0 && n_max > 0) {
             for (int t = 0; t < 2; t++) {
                 if (nb[t] == 0) continue;
-                mbar_arrive_expect_tx(q_full(t), kTile);
-                for (int c = 0; c < DC; c++) tma_load_4d(sQ + uint32_t(t) * kTile + uint32_t(c) * 16384u, &tmQ, q_full(t), c * 64, q0[t], h, b);
+                mbar_arrive_expect_tx(q_full(t), QP * kTile);
+                for (int pl = 0; pl < QP; pl++)
+                    for (int c = 0; c < DC; c++)
+                        tma_load_4d(sQ + uint32_t(t * QP + pl) * kTile + uint32_t(c) * 16384u, pl ? &tmQl : &tmQ, q_full(t), c * 64, q0[t], h, b);
             }
-            for (int i = 0; i < 2 * n_max; i++) {  // i = 2j: K_j, i = 2j+1: V_j
+            for (int i = 0; i < EB * n_max; i++) {  // entry e = i % EB of block j = i / EB
                 const int s = i % NS;
                 const uint32_t ph = uint32_t(i / NS) & 1u;
                 if (!mbar_wait(kv_empty(s), ph ^ 1u)) { attn_timeout(p.status, 31); break; }
                 mbar_arrive_expect_tx(kv_full(s), kTile);
-                const CUtensorMap* m = (i & 1) ? &tmV : &tmK;
+                const int e = i % EB;
+                const CUtensorMap* m = SPLIT ? (e == 0 ? &tmK : e == 1 ? &tmKl : e == 2 ? &tmV : &tmVl) : (e ? &tmV : &tmK);
                 for (int c = 0; c < DC; c++)
-                    tma_load_4d(sKV + uint32_t(s) * kTile + uint32_t(c) * 16384u, m, kv_full(s), c * 64, (i >> 1) * kBKV, h, b);
+                    tma_load_4d(sKV + uint32_t(s) * kTile + uint32_t(c) * 16384u, m, kv_full(s), c * 64, (i / EB) * kBKV, h, b);
             }
         }
     } else if (warp == 1) {
@@ -454,14 +470,25 @@ __global__ void __launch_bounds__(320, 1)
                 tc_fence_after();
                 return sKV + uint32_t(s) * kTile;
             };
-            auto issue_qk = [&](int t, uint32_t kb) {
+            // Q K^T of tile t: hi*hi, plus the two cross terms for fp32 operands (small terms first)
+            auto issue_qk = [&](int t, uint32_t kb_hi, uint32_t kb_lo) {
                 const uint32_t d_tmem = tmem_base + uint32_t(t) * 128u;
-                const uint32_t qb = sQ + uint32_t(t) * kTile;
+                const uint32_t q_hi = sQ + uint32_t(t * QP) * kTile;
+                const uint32_t q_lo = q_hi + kTile;
+                uint32_t acc = 0;
+                auto product = [&](uint32_t qb, uint32_t kb) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; kk++) {
-                    const uint32_t off = uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u;
-                    umma_f16_ss(d_tmem, make_smem_desc(qb + off, 16u, 1024u), make_smem_desc(kb + off, 16u, 1024u), idesc_qk, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u;
+                        umma_f16_ss(d_tmem, make_smem_desc(qb + off, 16u, 1024u), make_smem_desc(kb + off, 16u, 1024u), idesc_qk, acc);
+                        acc = 1;
+                    }
+                };
+                if (SPLIT) {
+                    product(q_lo, kb_hi);
+                    product(q_hi, kb_lo);
                 }
+                product(q_hi, kb_hi);
                 umma_commit(s_full(t));
             };
             for (int t = 0; t < 2 && ok; t++) {
@@ -469,18 +496,26 @@ __global__ void __launch_bounds__(320, 1)
                 if (!mbar_wait(q_full(t), 0)) { attn_timeout(p.status, 33); ok = false; }
             }
             if (ok) {
-                const uint32_t k0 = wait_slot(0);
+                const uint32_t k_hi = wait_slot(0);
+                const uint32_t k_lo = (SPLIT && ok) ? wait_slot(1) : 0u;
                 if (ok) {
-                    for (int t = 0; t < 2; t++) if (nb[t] > 0) issue_qk(t, k0);
+                    for (int t = 0; t < 2; t++) if (nb[t] > 0) issue_qk(t, k_hi, k_lo);
                     umma_commit(kv_empty(0 % NS));
+                    if (SPLIT) umma_commit(kv_empty(1 % NS));
                 }
             }
             for (int j = 0; j < n_max && ok; j++) {
-                const uint32_t vb = wait_slot(2 * j + 1);
+                const int iv = EB * j + (SPLIT ? 2 : 1);      // first V entry of block j
+                const int ik = EB * (j + 1);                  // first K entry of block j+1
+                const uint32_t v_hi = wait_slot(iv);
                 if (!ok) break;
-                uint32_t kb_next = 0;
+                const uint32_t v_lo = SPLIT ? wait_slot(iv + 1) : 0u;
+                if (!ok) break;
+                uint32_t k_hi = 0, k_lo = 0;
                 if (j + 1 < n_max) {
-                    kb_next = wait_slot(2 * j + 2);
+                    k_hi = wait_slot(ik);
+                    if (!ok) break;
+                    if (SPLIT) k_lo = wait_slot(ik + 1);
                     if (!ok) break;
                 }
                 for (int t = 0; t < 2 && ok; t++) {
@@ -488,18 +523,32 @@ __global__ void __launch_bounds__(320, 1)
                     if (!mbar_wait(p_full(t), uint32_t(j) & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
                     tc_fence_after();
                     const uint32_t o_tmem = tmem_base + 256u + uint32_t(t) * 128u;
-                    const uint32_t p_tmem = tmem_base + uint32_t(t) * 128u;  // P_t over the first 64 columns of S_t
+                    const uint32_t p_hi = tmem_base + uint32_t(t) * 128u;  // P_t over the first 64 columns of S_t
+                    const uint32_t p_lo = p_hi + 64u;                       // (fp32 path) low part over the last 64
+                    uint32_t acc = j > 0 ? 1u : 0u;
+                    auto product = [&](uint32_t pa, uint32_t vb) {
 #pragma unroll
-                    for (int kk = 0; kk < kBKV / 16; kk++) {
-                        const uint64_t db = make_smem_desc(vb + uint32_t(kk) * 2048u, 16384u, 1024u);
-                        umma_f16_ts(o_tmem, p_tmem + uint32_t(kk) * 8u, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < kBKV / 16; kk++) {
+                            const uint64_t db = make_smem_desc(vb + uint32_t(kk) * 2048u, 16384u, 1024u);
+                            umma_f16_ts(o_tmem, pa + uint32_t(kk) * 8u, db, idesc_pv, acc);
+                            acc = 1;
+                        }
+                    };
+                    if (SPLIT) {
+                        product(p_lo, v_hi);
+                        product(p_hi, v_lo);
                     }
+                    product(p_hi, v_hi);
                     umma_commit(o_full(t));
-                    if (j + 1 < nb[t]) issue_qk(t, kb_next);
+                    if (j + 1 < nb[t]) issue_qk(t, k_hi, k_lo);
                 }
                 if (!ok) break;
-                umma_commit(kv_empty((2 * j + 1) % NS));
-                if (j + 1 < n_max) umma_commit(kv_empty((2 * j + 2) % NS));
+                umma_commit(kv_empty(iv % NS));
+                if (SPLIT) umma_commit(kv_empty((iv + 1) % NS));
+                if (j + 1 < n_max) {
+                    umma_commit(kv_empty(ik % NS));
+                    if (SPLIT) umma_commit(kv_empty((ik + 1) % NS));
+                }
             }
         }
     } else {
@@ -566,6 +615,7 @@ __global__ void __launch_bounds__(320, 1)
             }
             const float m_ref = (m == -INFINITY) ? 0.f : m;
             float bl = 0.f;
+            uint32_t pk_lo[SPLIT ? 64 : 1];  // low parts wait in registers: their columns still hold unread scores
 #pragma unroll
             for (int c = 0; c < kBKV / 32; c++) {
                 uint32_t sv[32];
@@ -582,9 +632,22 @@ __global__ void __launch_bounds__(320, 1)
                     }
                     bl += x0 + x1;
                     pk[i] = pack2<IS_BF16>(x0, x1);
+                    if (SPLIT) {
+                        const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
+                        pk_lo[c * 16 + i] = pack2<true>(x0 - h0, x1 - h1);
+                    }
                 }
                 // keys 32c..32c+31 -> columns 16c..16c+15 of S_t (already consumed: they held keys < 32(c/2+1))
                 tmem_st_x16(s_addr + uint32_t(c) * 16u, pk);
+            }
+            if (SPLIT) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t part[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) part[i] = pk_lo[c * 16 + i];
+                    tmem_st_x16(s_addr + 64u + uint32_t(c) * 16u, part);
+                }
             }
             l += bl;
             tmem_st_wait();
@@ -600,7 +663,7 @@ __global__ void __launch_bounds__(320, 1)
             }
             tc_fence_after();
         }
-        using T = typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type;
+        using T = typename std::conditional<SPLIT, float, typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type>::type;
         const float inv = l > 0.f ? 1.f / l : 0.f;
         T* optr = static_cast<T*>(p.O) + b * p.os_b + h * p.os_h + (long long)row * p.os_s;
         if (q0[t] < p.Sq) {
@@ -614,7 +677,17 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = 0u;
                 }
-                if (row < p.Sq) {
+                if (row < p.Sq && SPLIT) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 8; v4++) {
+                        float4 w;
+                        w.x = __uint_as_float(o[v4 * 4 + 0]) * inv;
+                        w.y = __uint_as_float(o[v4 * 4 + 1]) * inv;
+                        w.z = __uint_as_float(o[v4 * 4 + 2]) * inv;
+                        w.w = __uint_as_float(o[v4 * 4 + 3]) * inv;
+                        *reinterpret_cast<float4*>(reinterpret_cast<float*>(optr) + c * 32 + v4 * 4) = w;
+                    }
+                } else if (row < p.Sq) {
 #pragma unroll
                     for (int v4 = 0; v4 < 4; v4++) {
                         uint4 w;
@@ -622,7 +695,7 @@ __global__ void __launch_bounds__(320, 1)
                         w.y = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
                         w.z = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
                         w.w = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = w;
+                        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(optr) + c * 32 + v4 * 8) = w;
                     }
                 }
             }
@@ -637,22 +710,45 @@ __global__ void __launch_bounds__(320, 1)
     }
 }
 
-bool g_attr2_done[16][4] = {};
+bool g_attr2_done[16][6] = {};
 
-template <int D, bool IS_BF16>
-int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-            const AttnKernelParams& kp, int slot) {
+template <int D, bool IS_BF16, bool SPLIT>
+int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, const AttnKernelParams& kp, int slot) {
     constexpr int kTileBytes = (D / 64) * 16384;
-    constexpr int NS = (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes > 8 ? 8 : (227 * 1024 - 2048 - 2 * kTileBytes) / kTileBytes;
-    constexpr size_t smem = size_t(kTileBytes) * (2 + NS) + 1024 + 256;
-    auto kern = attention_tc2_kernel<D, IS_BF16>;
+    constexpr int NS = attn2_slots(D, SPLIT);
+    constexpr size_t smem = size_t(kTileBytes) * (2 * (SPLIT ? 2 : 1) + NS) + 1024 + 256;
+    auto kern = attention_tc2_kernel<D, IS_BF16, SPLIT>;
     if (!g_attr2_done[ctx->device & 15][slot]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         g_attr2_done[ctx->device & 15][slot] = true;
     }
     const int64_t grid = p.B * p.H * ((kp.n_qtiles + 1) / 2);
-    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(tq, tk, tv, kp);
+    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
     return after_launch(ctx, "attention_tc2_kernel");
+}
+
+// fp32 [B,H,S,D] (strided, D contiguous) -> contiguous bf16 hi / lo planes.
+__global__ void __launch_bounds__(256) split_heads_kernel(const float* __restrict__ X, long long sb, long long sh, long long ss,
+                                                          int H, int S, int D, long long total4, __nv_bfloat16* __restrict__ hi,
+                                                          __nv_bfloat16* __restrict__ lo) {
+    const int d4 = D / 4;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+        const int dq = int(i % d4);
+        long long r = i / d4;
+        const int s = int(r % S); r /= S;
+        const int h = int(r % H);
+        const long long b = r / H;
+        const float4 x = *reinterpret_cast<const float4*>(X + b * sb + h * sh + s * ss + dq * 4);
+        const float xs[4] = {x.x, x.y, x.z, x.w};
+        Pack<__nv_bfloat16, 4> ph, pl;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            ph.v[e] = __float2bfloat16_rn(xs[e]);
+            pl.v[e] = __float2bfloat16_rn(xs[e] - __bfloat162float(ph.v[e]));
+        }
+        *reinterpret_cast<Pack<__nv_bfloat16, 4>*>(hi + i * 4) = ph;
+        *reinterpret_cast<Pack<__nv_bfloat16, 4>*>(lo + i * 4) = pl;
+    }
 }
 
 bool g_attr_done[16][4] = {};
@@ -710,11 +806,61 @@ int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, c
     const bool bf = p.prec == DOCC_B200_PREC_B;
     static const bool single_tile = [] { const char* e = getenv("DOCC_B200_ATTENTION_SINGLE_TILE"); return e && e[0] == '1'; }();
     if (!single_tile && p.Sq > kBQ) {
-        if (p.D == 128) return bf ? launch2<128, true>(ctx, p, tq, tk, tv, kp, 0) : launch2<128, false>(ctx, p, tq, tk, tv, kp, 1);
-        return bf ? launch2<64, true>(ctx, p, tq, tk, tv, kp, 2) : launch2<64, false>(ctx, p, tq, tk, tv, kp, 3);
+        const CUtensorMap maps[6] = {tq, tk, tv, tq, tk, tv};
+        if (p.D == 128) return bf ? launch2<128, true, false>(ctx, p, maps, kp, 0) : launch2<128, false, false>(ctx, p, maps, kp, 1);
+        return bf ? launch2<64, true, false>(ctx, p, maps, kp, 2) : launch2<64, false, false>(ctx, p, maps, kp, 3);
     }
     if (p.D == 128) return bf ? launch<128, true>(ctx, p, tq, tk, tv, kp, 0) : launch<128, false>(ctx, p, tq, tk, tv, kp, 1);
     return bf ? launch<64, true>(ctx, p, tq, tk, tv, kp, 2) : launch<64, false>(ctx, p, tq, tk, tv, kp, 3);
+}
+
+// fp32 attention on the tensor cores: operands split into bf16 hi/lo planes, three products per contraction.
+int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O) {
+    if (p.D != 64) return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc_f32: head_dim %lld (64 only)", (long long)p.D);
+    if (p.Skv <= 0 || p.Sq <= 0 || !(p.scale > 0.f)) return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc_f32: empty sequence or scale");
+    auto ok_in = [](const void* ptr, const int64_t* s) {
+        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && s[0] % 4 == 0 && s[1] % 4 == 0 && s[2] % 4 == 0;
+    };
+    if (!ok_in(Q, p.qs) || !ok_in(K, p.ks) || !ok_in(V, p.vs) || !ok_in(O, p.os))
+        return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc_f32: strides are not multiples of 16 bytes");
+    if (p.B * p.H * ceil_div(p.Sq, kBQ) > 0x7fffffff || p.Sq > INT32_MAX / 2 || p.Skv > INT32_MAX / 2)
+        return set_error(DOCC_B200_ERR_UNSUPPORTED, "attention_tc_f32: extent too large");
+    const size_t nq = size_t(p.B * p.H * p.Sq * p.D), nk = size_t(p.B * p.H * p.Skv * p.D);
+    void* ws;
+    DOCC_TRY(get_workspace(ctx, 3, (2 * nq + 4 * nk) * sizeof(__nv_bfloat16), &ws));
+    __nv_bfloat16* planes[6];  // q_hi, k_hi, v_hi, q_lo, k_lo, v_lo
+    __nv_bfloat16* base = static_cast<__nv_bfloat16*>(ws);
+    planes[0] = base; planes[3] = base + nq;
+    planes[1] = base + 2 * nq; planes[4] = planes[1] + nk;
+    planes[2] = planes[4] + nk; planes[5] = planes[2] + nk;
+    const void* src[3] = {Q, K, V};
+    const int64_t* str[3] = {p.qs, p.ks, p.vs};
+    const int64_t seq[3] = {p.Sq, p.Skv, p.Skv};
+    for (int i = 0; i < 3; i++) {
+        const long long total4 = (long long)(p.B * p.H * seq[i] * p.D / 4);
+        long long blocks = (total4 + 255) / 256;
+        if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+        split_heads_kernel<<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(src[i]), str[i][0], str[i][1], str[i][2],
+                                                                      int(p.H), int(seq[i]), int(p.D), total4, planes[i], planes[3 + i]);
+        DOCC_TRY(after_launch(ctx, "split_heads_kernel"));
+    }
+    CUtensorMap maps[6];
+    for (int i = 0; i < 6; i++) {
+        const int64_t S = seq[i % 3];
+        const uint64_t dims[4] = {uint64_t(p.D), uint64_t(S), uint64_t(p.H), uint64_t(p.B)};
+        const uint64_t strides[3] = {uint64_t(p.D) * 2, uint64_t(S * p.D) * 2, uint64_t(p.H * S * p.D) * 2};
+        const uint32_t box[4] = {64, 128, 1, 1};
+        DOCC_TRY(encode_tmap_16bit(&maps[i], planes[i], 4, dims, strides, box));
+    }
+    AttnKernelParams kp;
+    kp.Sq = int(p.Sq); kp.Skv = int(p.Skv); kp.H = int(p.H);
+    kp.n_qtiles = int(ceil_div(p.Sq, kBQ));
+    kp.causal = p.causal;
+    kp.causal_off = int(p.Skv - p.Sq);
+    kp.scale_log2 = p.scale * 1.4426950408889634f;
+    kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
+    kp.status = ctx->status_dev;
+    return launch2<64, true, true>(ctx, p, maps, kp, 4);
 }
 
 }  // namespace docc_b200
