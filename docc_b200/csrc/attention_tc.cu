@@ -576,21 +576,36 @@ __global__ void __launch_bounds__(320, 1)
             tc_fence_after();
             const bool need_mask = (k0 + kBKV > p.Skv) || (p.causal && k0 + kBKV - 1 > q0[t] + p.causal_off);
             const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;
-            float bm = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < kBKV / 32; c++) {
-                uint32_t sv[32];
-                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
-                tmem_ld_wait();
+            // Pass 1 (block maximum) with two chunk loads in flight: the next 32 columns are requested
+            // before the current ones are reduced, so the TMEM read latency overlaps the arithmetic.
+            // four independent running maxima / sums: a single chain of 128 dependent operations would
+            // leave the two warps per scheduler waiting on arithmetic latency
+            float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            uint32_t sa[32], sb[32];
+            auto max_chunk = [&](const uint32_t (&sv)[32], int c) {
                 if (need_mask) {
 #pragma unroll
                     for (int i = 0; i < 32; i++)
-                        if (c * 32 + i <= visible) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                        if (c * 32 + i <= visible) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(sv[i]));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) bm = fmaxf(bm, __uint_as_float(sv[i]));
+                    for (int i = 0; i < 32; i++) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(sv[i]));
                 }
-            }
+            };
+            tmem_ld_x32(s_addr, sa);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 32u, sb);
+            max_chunk(sa, 0);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 64u, sa);
+            max_chunk(sb, 1);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 96u, sb);
+            max_chunk(sa, 2);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr, sa);  // first chunk of pass 2
+            max_chunk(sb, 3);
+            const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
             const float m_cand = fmaxf(m, bm * p.scale_log2);
             // raise the reference maximum only when it moved by more than 8 (a factor 256 of headroom)
             const bool raise = m_cand > m + 8.0f;  // also true on the first block (m = -inf) when any key is visible
@@ -614,13 +629,9 @@ __global__ void __launch_bounds__(320, 1)
                 m = m_new;
             }
             const float m_ref = (m == -INFINITY) ? 0.f : m;
-            float bl = 0.f;
+            float bl4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk_lo[SPLIT ? 64 : 1];  // low parts wait in registers: their columns still hold unread scores
-#pragma unroll
-            for (int c = 0; c < kBKV / 32; c++) {
-                uint32_t sv[32];
-                tmem_ld_x32(s_addr + uint32_t(c) * 32u, sv);
-                tmem_ld_wait();
+            auto exp_chunk = [&](const uint32_t (&sv)[32], int c) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
@@ -630,7 +641,7 @@ __global__ void __launch_bounds__(320, 1)
                         if (c * 32 + 2 * i > visible) x0 = 0.f;
                         if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
                     }
-                    bl += x0 + x1;
+                    bl4[i & 3] += x0 + x1;
                     pk[i] = pack2<IS_BF16>(x0, x1);
                     if (SPLIT) {
                         const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
@@ -639,7 +650,20 @@ __global__ void __launch_bounds__(320, 1)
                 }
                 // keys 32c..32c+31 -> columns 16c..16c+15 of S_t (already consumed: they held keys < 32(c/2+1))
                 tmem_st_x16(s_addr + uint32_t(c) * 16u, pk);
-            }
+            };
+            // Pass 2, same two-deep pipeline (chunk 0 was requested at the end of pass 1; the rescale branch
+            // above waited for it if it ran, which is harmless).
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 32u, sb);
+            exp_chunk(sa, 0);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 64u, sa);
+            exp_chunk(sb, 1);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 96u, sb);
+            exp_chunk(sa, 2);
+            tmem_ld_wait();
+            exp_chunk(sb, 3);
             if (SPLIT) {
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
@@ -649,7 +673,7 @@ __global__ void __launch_bounds__(320, 1)
                     tmem_st_x16(s_addr + 64u + uint32_t(c) * 16u, part);
                 }
             }
-            l += bl;
+            l += (bl4[0] + bl4[1]) + (bl4[2] + bl4[3]);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
