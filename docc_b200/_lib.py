@@ -76,12 +76,13 @@ class DoccB200Error(RuntimeError):
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("DOCC_B200_RT_LIB", LIB_PATH)  # a differently built runtime may be substituted
+        if not os.path.exists(path):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: the CUDA runtime library has not been built. "
+                f"{path} is missing: the CUDA runtime library has not been built. "
                 "Run `python -m docc_b200.build` (needs nvcc); there is no CPU fallback."
             )
-        handle = ctypes.CDLL(LIB_PATH)
+        handle = ctypes.CDLL(path)
         for name, (restype, argtypes) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype = restype

@@ -471,16 +471,19 @@ __global__ void __launch_bounds__(320, 1)
                 return sKV + uint32_t(s) * kTile;
             };
             // Q K^T of tile t: hi*hi, plus the two cross terms for fp32 operands (small terms first)
+            // Descriptors are built once per operand tile; the k-steps only add a constant to the address
+            // field (16-byte units), which keeps the issuing thread ahead of the tensor pipe.
             auto issue_qk = [&](int t, uint32_t kb_hi, uint32_t kb_lo) {
                 const uint32_t d_tmem = tmem_base + uint32_t(t) * 128u;
-                const uint32_t q_hi = sQ + uint32_t(t * QP) * kTile;
-                const uint32_t q_lo = q_hi + kTile;
+                const uint64_t q_hi = make_smem_desc(sQ + uint32_t(t * QP) * kTile, 16u, 1024u);
+                const uint64_t q_lo = q_hi + uint64_t(kTile >> 4);
                 uint32_t acc = 0;
-                auto product = [&](uint32_t qb, uint32_t kb) {
+                auto product = [&](uint64_t qd, uint32_t kb) {
+                    const uint64_t kd = make_smem_desc(kb, 16u, 1024u);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t off = uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u;
-                        umma_f16_ss(d_tmem, make_smem_desc(qb + off, 16u, 1024u), make_smem_desc(kb + off, 16u, 1024u), idesc_qk, acc);
+                        const uint64_t off = uint64_t((uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u) >> 4);
+                        umma_f16_ss(d_tmem, qd + off, kd + off, idesc_qk, acc);
                         acc = 1;
                     }
                 };
@@ -527,10 +530,10 @@ __global__ void __launch_bounds__(320, 1)
                     const uint32_t p_lo = p_hi + 64u;                       // (fp32 path) low part over the last 64
                     uint32_t acc = j > 0 ? 1u : 0u;
                     auto product = [&](uint32_t pa, uint32_t vb) {
+                        const uint64_t vd = make_smem_desc(vb, 16384u, 1024u);
 #pragma unroll
                         for (int kk = 0; kk < kBKV / 16; kk++) {
-                            const uint64_t db = make_smem_desc(vb + uint32_t(kk) * 2048u, 16384u, 1024u);
-                            umma_f16_ts(o_tmem, pa + uint32_t(kk) * 8u, db, idesc_pv, acc);
+                            umma_f16_ts(o_tmem, pa + uint32_t(kk) * 8u, vd + uint64_t(kk * (2048 / 16)), idesc_pv, acc);
                             acc = 1;
                         }
                     };
