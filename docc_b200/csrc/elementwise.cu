@@ -82,13 +82,17 @@ __global__ void __launch_bounds__(BLOCK) layernorm_kernel(const T* __restrict__ 
             const int64_t p = int64_t(i) * TPR + t;
             if (ok && p < packs) {
                 P pk;
+                // gamma / beta as 16-byte vectors (VEC is 4 or 8 and the arrays are 16-byte aligned here)
+                float gm[VEC], bt[VEC];
 #pragma unroll
-                for (int e = 0; e < VEC; e++) {
-                    const int64_t c = p * VEC + e;
-                    const float gm = gamma ? gamma[c] : 1.f;
-                    const float bt = beta ? beta[c] : 0.f;
-                    pk.v[e] = from_float<T>((v[i][e] - mean) * rstd * gm + bt);
+                for (int q4 = 0; q4 < VEC / 4; q4++) {
+                    const float4 g4 = gamma ? __ldg(reinterpret_cast<const float4*>(gamma + p * VEC) + q4) : make_float4(1.f, 1.f, 1.f, 1.f);
+                    const float4 b4 = beta ? __ldg(reinterpret_cast<const float4*>(beta + p * VEC) + q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    gm[q4 * 4 + 0] = g4.x; gm[q4 * 4 + 1] = g4.y; gm[q4 * 4 + 2] = g4.z; gm[q4 * 4 + 3] = g4.w;
+                    bt[q4 * 4 + 0] = b4.x; bt[q4 * 4 + 1] = b4.y; bt[q4 * 4 + 2] = b4.z; bt[q4 * 4 + 3] = b4.w;
                 }
+#pragma unroll
+                for (int e = 0; e < VEC; e++) pk.v[e] = from_float<T>((v[i][e] - mean) * rstd * gm[e] + bt[e]);
                 store_pack(yr + p, pk);
             }
         }
@@ -132,7 +136,8 @@ template <typename T>
 int layernorm_device(Ctx* ctx, int64_t rows, int64_t cols, const T* X, const float* g, const float* b, double eps, T* Y) {
     if (rows == 0 || cols == 0) return DOCC_B200_OK;
     constexpr int VEC = 16 / sizeof(T);
-    const bool aligned = cols % VEC == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && reinterpret_cast<uintptr_t>(Y) % 16 == 0;
+    const bool aligned = cols % VEC == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && reinterpret_cast<uintptr_t>(Y) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(g) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0;
     const int64_t packs = cols / VEC;
     if (aligned && packs <= 2048) {
         if (packs <= 32) return launch_ln<T, 1, 32>(ctx, X, g, b, float(eps), Y, rows, cols);

@@ -420,3 +420,46 @@ def test_launch_counter_counts_our_kernels(rt):
     ops.softmax(torch.randn(64, 256, device="cuda"), [-1])
     ops.sync()
     assert ops.launch_count() == 1
+
+
+def test_concurrent_host_threads(rt):
+    # generated code is entered from arbitrary Python threads with the GIL released
+    # (compiled_sdfg.py:447): every thread gets its own context and stream, the pool is shared
+    import threading
+
+    rng = np.random.RandomState(12)
+    jobs = []
+    for i in range(4):
+        a, b = rng.rand(150 + i, 90), rng.rand(90, 70 + i)
+        x = (rng.randn(64, 300 + 16 * i) * 3).astype(np.float32)
+        jobs.append((a, b, x))
+    results = [None] * len(jobs)
+
+    def worker(i):
+        a, b, x = jobs[i]
+        out = []
+        for _ in range(5):
+            out.append((ops.gemm(a, b), ops.softmax(x, [-1])))  # host pointers: staged through the shared pool
+        results[i] = out
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(jobs))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for (a, b, x), outs in zip(jobs, results):
+        for c, y in outs:
+            assert relerr(c, a @ b) <= TOL_F64
+            assert relerr(y, oracle.softmax(x, [-1])) <= TOL_F32
+
+
+def test_device_array_keeps_intermediates_on_the_device(rt):
+    rng = np.random.RandomState(13)
+    a, b = rng.rand(40, 30), rng.rand(30, 20)
+    da, db = ops.DeviceArray.from_numpy(a), ops.DeviceArray.from_numpy(b)
+    dc = ops.gemm(da, db)
+    dy = ops.softmax(dc, [1])
+    assert isinstance(dy, ops.DeviceArray)
+    assert relerr(dy.to_numpy(), oracle.softmax(oracle.gemm(a, b), [1])) <= 1e-12
+    with pytest.raises(TypeError):
+        ops.gemm(da, b)  # device and host operands do not mix
