@@ -621,6 +621,7 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
     // k-block's flops per loaded byte are high: 256x256 tiles (131 flop/B) run at full rate,
     // 128x256 at ~0.68, 128x128 at ~0.5. Small problems prefer more, smaller tiles. Pick the
     // candidate with the lowest (waves x tile area / efficiency).
+    const bool heavy_epilogue = ep.bias || ep.act != DOCC_B200_ACT_NONE || ep.residual || ep.beta != 0.f;
     int bm = 128, bn;
     if (N <= 64) {
         bn = p.b_kmajor ? int(ceil_div(N, 16) * 16) : 64;
@@ -631,8 +632,9 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         for (const auto& c : cand) {
             if (c.bm == 256 && M <= 128) continue;
             // a 256-row tile owns all of TMEM, so its epilogue does not overlap the next main loop:
-            // only worth it when the main loop is long
-            if (c.bm == 256 && K * npass < 2048) continue;
+            // only worth it when the main loop is long (longer still when the drain also has to load
+            // bias / residual or evaluate an activation)
+            if (c.bm == 256 && K * npass < (heavy_epilogue ? 2048 : 1024)) continue;
             if (c.bn > 64 && c.bn / 2 >= N) continue;
             const int64_t tiles = ceil_div(M, c.bm) * ceil_div(N, c.bn) * batch;
             const double cost = double(ceil_div(tiles, ctx->sm_count)) * c.bm * c.bn / c.eff;
