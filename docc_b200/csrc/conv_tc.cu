@@ -120,32 +120,41 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int kb_per_pass = p.kh * p.kw * cblocks;
 
     if (warp == 0) {
+        // TMA producer. A single lane issues, so the k-block loop is a (tap row, tap column, channel block) nest with
+        // an incrementally kept ring position: no division between two loads.
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;
             long long u = u_begin;
             Tile t;
             bool ok = true;
+            const uint32_t row_bytes = uint32_t(p.Wo) * 128u;
             while (ok && next_tile(p, u, u_end, t)) {
-                const uint32_t tx = kABytes + uint32_t(t.rows) * uint32_t(p.Wo) * 128u;
+                const uint32_t tx = kABytes + uint32_t(t.rows) * row_bytes;
                 for (int pass = 0; pass < p.npass && ok; pass++) {
                     const CUtensorMap* mw = p.pw[pass] ? &tmW1 : &tmW0;
                     const CUtensorMap* mx = p.px[pass] ? &tmX1 : &tmX0;
-                    for (int kb = 0; kb < kb_per_pass; kb++, it++) {
-                        const int s = int(it % kStages);
-                        const uint32_t ph = (it / kStages) & 1u;
-                        if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
-                            conv_timeout(p.status, 21);
-                            ok = false;
-                            break;
+                    int k_col = 0;  // column of this k-block in the re-laid weights: (tap * cblocks + cb) * 64
+                    for (int ky = 0; ky < p.kh && ok; ky++) {
+                        const int ih0 = t.oh0 + ky - p.pad_h;
+                        for (int kx = 0; kx < p.kw && ok; kx++) {
+                            const int iw0 = kx - p.pad_w;
+                            for (int c0 = 0; c0 < p.C; c0 += 64, k_col += 64) {
+                                const uint32_t full = full_bar(0) + 8u * s;
+                                if (!mbar_wait(empty_bar(0) + 8u * s, ph ^ 1u)) {
+                                    conv_timeout(p.status, 21);
+                                    ok = false;
+                                    break;
+                                }
+                                mbar_arrive_expect_tx(full, tx);
+                                tma_load_2d(sA + s * kABytes, mw, full, k_col, t.m0);
+                                uint32_t b_dst = sB + s * kBBytes;
+                                for (int r = 0; r < t.rows; r++, b_dst += row_bytes) tma_load_4d(b_dst, mx, full, c0, iw0, ih0 + r, t.n);
+                                if (++s == uint32_t(kStages)) {
+                                    s = 0;
+                                    ph ^= 1u;
+                                }
+                            }
                         }
-                        const int tap = kb / cblocks, cb = kb - tap * cblocks;
-                        const int ky = tap / p.kw, kx = tap - ky * p.kw;
-                        mbar_arrive_expect_tx(full_bar(s), tx);
-                        tma_load_2d(sA + uint32_t(s) * kABytes, mw, full_bar(s), kb * 64, t.m0);
-                        const uint32_t b_dst = sB + uint32_t(s) * kBBytes;
-                        for (int r = 0; r < t.rows; r++)
-                            tma_load_4d(b_dst + uint32_t(r) * uint32_t(p.Wo) * 128u, mx, full_bar(s), cb * 64, kx - p.pad_w,
-                                        t.oh0 + r + ky - p.pad_h, t.n);
                     }
                 }
             }
@@ -156,11 +165,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else if (warp == 1) {
+        // UMMA issuer: descriptors advance by adds, four k-steps per asm block.
         if (lane == 0) {
-            uint32_t it = 0, lt = 0;
+            uint32_t lt = 0;
             long long u = u_begin;
             Tile t;
             bool ok = true;
+            const int k_iters = p.npass * kb_per_pass;
+            const uint64_t a_desc0 = make_smem_desc(sA, 16u, 1024u), b_desc0 = make_smem_desc(sB, 16u, 1024u);
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            uint32_t s = 0, ph = 0;
             while (ok && next_tile(p, u, u_end, t)) {
                 const uint32_t buf = lt & 1u, use = lt >> 1;
                 lt++;
@@ -173,24 +187,23 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t idesc = make_idesc(128, n_mma, 1, 0, 0);
                 const uint32_t d_tmem = tmem_base + buf * 256u;
                 uint32_t acc = 0;
-                for (int pass = 0; pass < p.npass && ok; pass++) {
-                    for (int kb = 0; kb < kb_per_pass; kb++, it++) {
-                        const int s = int(it % kStages);
-                        const uint32_t ph = (it / kStages) & 1u;
-                        if (!mbar_wait(full_bar(s), ph)) {
-                            conv_timeout(p.status, 23);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        const uint32_t a_base = sA + uint32_t(s) * kABytes, b_base = sB + uint32_t(s) * kBBytes;
-#pragma unroll
-                        for (int kk = 0; kk < 4; kk++) {
-                            umma_f16_ss(d_tmem, make_smem_desc(a_base + uint32_t(kk) * 32u, 16u, 1024u),
-                                        make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u), idesc, acc);
-                            acc = 1;
-                        }
-                        umma_commit(empty_bar(s));
+                for (int k = 0; k < k_iters; k++) {
+                    if (!mbar_wait(full_bar(0) + 8u * s, ph)) {
+                        conv_timeout(p.status, 23);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    umma_f16_ss_x4<1>(d_tmem, a_desc, b_desc, idesc, acc, 2, 2);  // +32 bytes per 16-deep k-step
+                    acc = 1;
+                    umma_commit(empty_bar(0) + 8u * s);
+                    a_desc += kABytes >> 4;
+                    b_desc += kBBytes >> 4;
+                    if (++s == uint32_t(kStages)) {
+                        s = 0;
+                        ph ^= 1u;
+                        a_desc = a_desc0;
+                        b_desc = b_desc0;
                     }
                 }
                 if (ok) umma_commit(tfull_bar(int(buf)));

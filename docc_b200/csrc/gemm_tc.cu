@@ -18,6 +18,8 @@
 // of tile i+1). fp32 operands are handled as split bf16 (hi + lo): the kernel runs up to three
 // passes (hi*hi, hi*lo, lo*hi) into the same accumulator, which keeps fp32-level accuracy
 // (~2^-16 relative per product) at a third of the bf16 rate. Every wait is bounded.
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "device_math.cuh"
@@ -294,9 +296,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
+        // One lane issues everything, so the loop keeps its ring position incrementally (no division per
+        // k-block): slot index, phase and destination addresses.
         if (lane == 0) {
-            uint32_t it = 0;
             bool ok = true;
+            uint32_t s = 0, ph = 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int b, m0, n0;
                 tile_coords(p, t, b, m0, n0);
@@ -304,29 +308,29 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int pass = 0; pass < p.npass && ok; pass++) {
                     const CUtensorMap* ma = p.pa[pass] ? &tmA1 : &tmA0;
                     const CUtensorMap* mb = p.pb[pass] ? &tmB1 : &tmB0;
-                    for (int kb = 0; kb < p.num_kb; kb++, it++) {
-                        const int s = int(it % uint32_t(p.stages));
-                        const uint32_t ph = (it / uint32_t(p.stages)) & 1u;
-                        if (!mbar_wait(empty_bar(s), ph ^ 1u)) {
+                    for (int k0 = 0; k0 < p.num_kb * kBK; k0 += kBK) {
+                        const uint32_t full = full_bar(0) + 8u * s;
+                        if (!mbar_wait(empty_bar(0) + 8u * s, ph ^ 1u)) {
                             report_timeout(p.status, 1);
                             ok = false;
                             break;
                         }
-                        mbar_arrive_expect_tx(full_bar(s), stage_tx);
-                        const uint32_t a_dst = sA + uint32_t(s) * p.a_bytes;
-                        const uint32_t b_dst = sB + uint32_t(s) * p.b_bytes;
-                        const int k0 = kb * kBK;
+                        mbar_arrive_expect_tx(full, stage_tx);
+                        const uint32_t a_dst = sA + s * p.a_bytes;
+                        const uint32_t b_dst = sB + s * p.b_bytes;
                         if (p.a_kmajor) {
-                            tma_load_3d(a_dst, ma, full_bar(s), k0, m0, ba);
+                            tma_load_3d(a_dst, ma, full, k0, m0, ba);
                         } else {
-                            for (int j = 0; j < p.bm / 64; j++)
-                                tma_load_3d(a_dst + uint32_t(j) * 8192u, ma, full_bar(s), m0 + 64 * j, k0, ba);
+                            for (int j = 0; j < p.bm / 64; j++) tma_load_3d(a_dst + uint32_t(j) * 8192u, ma, full, m0 + 64 * j, k0, ba);
                         }
                         if (p.b_kmajor) {
-                            tma_load_3d(b_dst, mb, full_bar(s), k0, n0, bb);
+                            tma_load_3d(b_dst, mb, full, k0, n0, bb);
                         } else {
-                            for (int j = 0; j < p.bn / 64; j++)
-                                tma_load_3d(b_dst + uint32_t(j) * 8192u, mb, full_bar(s), n0 + 64 * j, k0, bb);
+                            for (int j = 0; j < p.bn / 64; j++) tma_load_3d(b_dst + uint32_t(j) * 8192u, mb, full, n0 + 64 * j, k0, bb);
+                        }
+                        if (++s == uint32_t(p.stages)) {
+                            s = 0;
+                            ph ^= 1u;
                         }
                     }
                 }
@@ -340,55 +344,53 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else if (warp == 1) {
         // ---------------- UMMA issuer ----------------
+        // Also a single lane: descriptors advance by adds, the four 16-deep k-steps of a k-block go out in one asm block.
         if (lane == 0) {
-            uint32_t it = 0;
             uint32_t lt = 0;
             bool ok = true;
-            const int halves = tall ? 2 : 1;
-            const int last_it = p.npass * p.num_kb - 1;
+            const int k_iters = p.npass * p.num_kb;
+            // K-major tiles advance 32 bytes per k-step, MN-major tiles 2048 (16 rows of 128 bytes)
+            const uint64_t a_desc0 = p.a_kmajor ? make_smem_desc(sA, 16u, 1024u) : make_smem_desc(sA, 8192u, 1024u);
+            const uint64_t b_desc0 = p.b_kmajor ? make_smem_desc(sB, 16u, 1024u) : make_smem_desc(sB, 8192u, 1024u);
+            const uint64_t a_step = p.a_kmajor ? 2 : 128, b_step = p.b_kmajor ? 2 : 128;
+            const uint64_t a_stride = p.a_bytes >> 4, b_stride = p.b_bytes >> 4;  // per ring slot, in descriptor address units
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            uint32_t s = 0, ph = 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, lt++) {
+                // the epilogue must have drained the accumulator region(s) this tile overwrites
                 const uint32_t buf = tall ? 0u : (lt & 1u);
                 const uint32_t wait_parity = tall ? ((lt & 1u) ^ 1u) : (((lt >> 1) & 1u) ^ 1u);
-                int local_it = 0;
-                for (int pass = 0; pass < p.npass && ok; pass++) {
-                    for (int kb = 0; kb < p.num_kb; kb++, it++, local_it++) {
-                        const int s = int(it % uint32_t(p.stages));
-                        const uint32_t ph = (it / uint32_t(p.stages)) & 1u;
-                        if (!mbar_wait(full_bar(s), ph)) {
-                            report_timeout(p.status, 3);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after();
-                        const uint32_t a_base = sA + uint32_t(s) * p.a_bytes;
-                        const uint32_t b_base = sB + uint32_t(s) * p.b_bytes;
-                        for (int h = 0; h < halves && ok; h++) {
-                            const uint32_t region = tall ? uint32_t(h) : buf;
-                            if (local_it == 0) {
-                                // the epilogue must have drained this TMEM region before it is overwritten
-                                if (!mbar_wait(tempty_bar(int(region)), wait_parity)) {
-                                    report_timeout(p.status, 2);
-                                    ok = false;
-                                    break;
-                                }
-                                tc_fence_after();
-                            }
-                            const uint32_t d_tmem = tmem_base + region * 256u;
-                            const uint32_t a_half = a_base + uint32_t(h) * 16384u;  // 128 rows of either A layout
-#pragma unroll
-                            for (int kk = 0; kk < kBK / 16; kk++) {
-                                const uint64_t da = p.a_kmajor ? make_smem_desc(a_half + uint32_t(kk) * 32u, 16u, 1024u)
-                                                               : make_smem_desc(a_half + uint32_t(kk) * 2048u, 8192u, 1024u);
-                                const uint64_t db = p.b_kmajor ? make_smem_desc(b_base + uint32_t(kk) * 32u, 16u, 1024u)
-                                                               : make_smem_desc(b_base + uint32_t(kk) * 2048u, 8192u, 1024u);
-                                umma_f16_ss(d_tmem, da, db, p.idesc, (local_it > 0 || kk > 0) ? 1u : 0u);
-                            }
-                            if (local_it == last_it) umma_commit(tfull_bar(int(region)));  // accumulator region complete
-                        }
-                        if (!ok) break;
-                        umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                if (!mbar_wait(tempty_bar(int(buf)), wait_parity) || (tall && !mbar_wait(tempty_bar(1), wait_parity))) {
+                    report_timeout(p.status, 2);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int k = 0; k < k_iters; k++) {
+                    if (!mbar_wait(full_bar(0) + 8u * s, ph)) {
+                        report_timeout(p.status, 3);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    umma_f16_ss_x4<1>(d_tmem, a_desc, b_desc, p.idesc, acc, a_step, b_step);
+                    // tall: rows 128..255 of the A tile (16 KB further on in either layout) into the second region
+                    if (tall) umma_f16_ss_x4<1>(d_tmem + 256u, a_desc + (16384u >> 4), b_desc, p.idesc, acc, a_step, b_step);
+                    acc = 1;
+                    umma_commit(empty_bar(0) + 8u * s);  // frees the slot once these MMAs have read it
+                    a_desc += a_stride;
+                    b_desc += b_stride;
+                    if (++s == uint32_t(p.stages)) {
+                        s = 0;
+                        ph ^= 1u;
+                        a_desc = a_desc0;
+                        b_desc = b_desc0;
                     }
                 }
+                if (!ok) break;
+                umma_commit(tfull_bar(int(buf)));  // accumulator complete
+                if (tall) umma_commit(tfull_bar(1));
             }
         }
     } else {
@@ -440,6 +442,217 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- CTA-pair variant (cta_group::2) ------------------------------------------------------------------
+// A cluster of two CTAs owns a 256 x bn tile, bn = 256 or 512. Per k-block rank r loads rows
+// [128r, 128r+128) of the A tile and, for each 256-column block of the tile, rows [128r, 128r+128) of
+// that block of B: 32 KB (bn = 256) or 48 KB (bn = 512) per CTA, against 64 KB for a single-CTA 256x256
+// tile of the same arithmetic, which is what relieves the L2 -> SM fabric. The leader's UMMA thread issues
+// M = 256, N = 256 instructions for both CTAs; its commits release the stage in both and publish both
+// accumulator halves. Each CTA drains its own 128 accumulator rows through the same epilogue as the
+// single-CTA kernel and reports the drain to the leader. bn = 256 double-buffers the accumulator so the
+// drain overlaps the next main loop; bn = 512 fills tensor memory (no overlap: long K only).
+// Operands must be K-major.
+__global__ void __launch_bounds__(kThreads, 1)
+    tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                        const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmB1,
+                        const __grid_constant__ CUtensorMap tmOut, const TcKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    constexpr uint32_t kHalf = 128u * 128u;  // 128 rows x 64 bf16
+    const bool wide = p.bn == 512;
+    const int nh = wide ? 2 : 1;  // 256-column blocks per tile
+    const uint32_t b_stage = uint32_t(nh) * kHalf;
+    const uint32_t sA = base;
+    const uint32_t sB = sA + uint32_t(p.stages) * kHalf;
+    const uint32_t sStage = sB + uint32_t(p.stages) * b_stage;
+    const uint32_t bars = sStage + kStagingBytes;
+    auto full_bar = [&](int i) { return bars + 8u * uint32_t(i); };
+    auto empty_bar = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
+    auto tfull_bar = [&](int i) { return bars + 128u + 8u * uint32_t(i); };
+    auto tempty_bar = [&](int i) { return bars + 144u + 8u * uint32_t(i); };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 160u - raw_addr));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int n_pairs = gridDim.x >> 1;
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < p.stages; i++) {
+            mbar_init(full_bar(i), 1);   // waited on in the leader only: its producer's arrive + both CTAs' bytes
+            mbar_init(empty_bar(i), 1);  // one multicast commit per use
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(tfull_bar(i), 1);
+            // the leader's copy collects the drains of both CTAs: all eight epilogue warps of each for a
+            // double-buffered 256-column accumulator, one group of four per 256-column block when wide
+            mbar_init(tempty_bar(i), wide ? 8 : 16);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmA0);
+        prefetch_tensormap(&tmB0);
+        if (p.npass > 1) {
+            prefetch_tensormap(&tmA1);
+            prefetch_tensormap(&tmB1);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers are initialised before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int total_tiles = p.tiles_m * p.tiles_n * p.batch;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        // One lane issues everything, so the loop keeps its ring position incrementally (no division per
+        // k-block): slot index, phase, destination addresses and the leader's barrier address.
+        if (lane == 0) {
+            bool ok = true;
+            const uint32_t stage_tx = 2u * (kHalf + b_stage);  // both CTAs' A and B parts
+            const uint32_t lead_full0 = map_to_cta(full_bar(0), 0);
+            const int row_off = 128 * int(rank);
+            uint32_t s = 0, ph = 0;
+            for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+                int b, m0, n0;
+                tile_coords(p, t, b, m0, n0);
+                const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+                m0 += row_off;
+                n0 += row_off;
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    const CUtensorMap* ma = p.pa[pass] ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = p.pb[pass] ? &tmB1 : &tmB0;
+                    for (int k0 = 0; k0 < p.num_kb * kBK; k0 += kBK) {
+                        if (!mbar_wait(empty_bar(0) + 8u * s, ph ^ 1u)) {
+                            report_timeout(p.status, 41);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t lead_full = lead_full0 + 8u * s;
+                        if (leader) mbar_arrive_expect_tx(full_bar(0) + 8u * s, stage_tx);
+                        tma_load_3d_pair(sA + s * kHalf, ma, lead_full, k0, m0, ba);
+                        tma_load_3d_pair(sB + s * b_stage, mb, lead_full, k0, n0, bb);
+                        if (wide) tma_load_3d_pair(sB + s * b_stage + kHalf, mb, lead_full, k0, n0 + 256, bb);
+                        if (++s == uint32_t(p.stages)) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                // let copies already in flight land before the CTA retires
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer (leader only) ----------------
+        if (leader && lane == 0) {
+            uint32_t lt = 0;
+            bool ok = true;
+            const int k_iters = p.npass * p.num_kb;
+            const uint64_t a_desc0 = make_smem_desc(sA, 16u, 1024u), b_desc0 = make_smem_desc(sB, 16u, 1024u);
+            const uint64_t a_stride = kHalf >> 4, b_stride = b_stage >> 4;  // per ring slot, in descriptor address units
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            uint32_t s = 0, ph = 0;
+            for (int t = pair; t < total_tiles && ok; t += n_pairs, lt++) {
+                // both CTAs must have drained the accumulator region(s) this tile overwrites
+                const uint32_t buf = wide ? 0u : (lt & 1u);
+                const uint32_t wait_parity = wide ? ((lt & 1u) ^ 1u) : (((lt >> 1) & 1u) ^ 1u);
+                if (!mbar_wait(tempty_bar(int(buf)), wait_parity) || (wide && !mbar_wait(tempty_bar(1), wait_parity))) {
+                    report_timeout(p.status, 42);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int k = 0; k < k_iters; k++) {
+                    if (!mbar_wait(full_bar(0) + 8u * s, ph)) {
+                        report_timeout(p.status, 43);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    umma_f16_ss_x4<2>(d_tmem, a_desc, b_desc, p.idesc, acc, 2, 2);  // +32 bytes per 16-deep k-step
+                    if (wide) umma_f16_ss_x4<2>(d_tmem + 256u, a_desc, b_desc + (kHalf >> 4), p.idesc, acc, 2, 2);
+                    acc = 1;
+                    umma_commit_pair(empty_bar(0) + 8u * s, 3);  // both CTAs may refill the slot
+                    a_desc += a_stride;
+                    b_desc += b_stride;
+                    if (++s == uint32_t(p.stages)) {
+                        s = 0;
+                        ph ^= 1u;
+                        a_desc = a_desc0;
+                        b_desc = b_desc0;
+                    }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar(int(buf)), 3);  // accumulator complete in both CTAs
+                if (wide) umma_commit_pair(tfull_bar(1), 3);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps: this CTA's 128 rows of the tile ----------------
+        const int q = warp & 3;
+        const int wg = (warp - 2) >> 2;
+        uint32_t lt = 0;
+        for (int t = pair; t < total_tiles; t += n_pairs, lt++) {
+            int b, m0, n0;
+            tile_coords(p, t, b, m0, n0);
+            const uint32_t region = wide ? uint32_t(wg) : (lt & 1u);
+            const uint32_t parity = wide ? (lt & 1u) : ((lt >> 1) & 1u);
+            if (!mbar_wait(tfull_bar(int(region)), parity)) {
+                if (lane == 0) report_timeout(p.status, 44);
+                break;
+            }
+            tc_fence_after();
+            const int row0 = m0 + 128 * int(rank) + q * 32;
+            const long long row = row0 + lane;
+            // wide: accumulator column c is tile column c and group wg drains block wg; otherwise the
+            // groups split the 256 columns of the current buffer
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + (wide ? 0u : region * 256u);
+            const int c_begin = wide ? 256 * wg : (wg == 0 ? 0 : 128);
+            const int c_end = wide ? 256 * wg + 256 : (wg == 0 ? 128 : 256);
+            const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
+#define DOCC_EPI(T, A) epilogue_tile<T, A>(p, &tmOut, stage_base, t_addr, c_begin, c_end, row, row0, n0, b, lane)
+#define DOCC_EPI_ACT(T)                                                  \
+    do {                                                                 \
+        if (p.act == DOCC_B200_ACT_NONE) DOCC_EPI(T, 0);                 \
+        else if (p.act == DOCC_B200_ACT_GELU_ERF) DOCC_EPI(T, 1);        \
+        else if (p.act == DOCC_B200_ACT_RELU) DOCC_EPI(T, 2);            \
+        else DOCC_EPI(T, -1);                                            \
+    } while (0)
+            if (p.out_prec == DOCC_B200_PREC_S) DOCC_EPI_ACT(float);
+            else if (p.out_prec == DOCC_B200_PREC_B) DOCC_EPI_ACT(__nv_bfloat16);
+            else DOCC_EPI_ACT(__half);
+#undef DOCC_EPI_ACT
+#undef DOCC_EPI
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(int(region)), 0));
+        }
+        if (p.tma_out && lane == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // neither CTA retires while the other may still signal its barriers or read its tiles
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -528,6 +741,7 @@ int get_encode(EncodeFn* fn) {
 }
 
 bool g_attr_set[16] = {false};
+bool g_attr_pair_set[16] = {false};
 
 }  // namespace
 
@@ -645,6 +859,21 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
             }
         }
     }
+    // CTA pairs (cta_group::2) for large K-major problems: 256x256 tiles at half the shared-memory and, with
+    // 256x512 tiles on a long K, three quarters of the L2 -> SM traffic of the single-CTA kernel
+    static const int pair_mode = [] { const char* e = getenv("DOCC_B200_GEMM_PAIR"); return e ? atoi(e) : 1; }();
+    bool use_pair = pair_mode && p.a_kmajor && p.b_kmajor && M >= 256 && N >= 256 && ctx->sm_count % 2 == 0 && K * npass >= 512;
+    if (use_pair) {
+        const int pairs = ctx->sm_count / 2;
+        const int64_t t256 = ceil_div(M, 256) * ceil_div(N, 256) * batch, t512 = ceil_div(M, 256) * ceil_div(N, 512) * batch;
+        if (t256 < pairs) use_pair = false;
+        else {
+            bm = 256;
+            bn = 256;
+            const bool wide_ok = pair_mode == 2 || (pair_mode == 1 && K * npass >= 4096);
+            if (wide_ok && t512 >= pairs && double(ceil_div(t512, pairs)) * 512 <= double(ceil_div(t256, pairs)) * 256 * 1.05) bn = 512;
+        }
+    }
     p.bm = bm;
     p.bn = bn;
     p.a_bytes = uint32_t(bm) * 128u;
@@ -660,6 +889,14 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
     if (stages < 2) stages = 2;
     p.stages = stages;
     p.idesc = make_idesc(128, bn, ab_format, p.a_kmajor ? 0 : 1, p.b_kmajor ? 0 : 1);
+    if (use_pair) {
+        stages = (kSmemBudget - 2048 - int(kStagingBytes)) / ((1 + bn / 256) * 128 * 128);
+        if (stages > kMaxStages) stages = kMaxStages;
+        if (stages > k_iters && k_iters >= 2) stages = int(k_iters);
+        if (stages < 2) stages = 2;
+        p.stages = stages;
+        p.idesc = make_idesc(256, 256, ab_format, 0, 0);
+    }
 
     p.alpha = ep.alpha; p.beta = ep.beta;
     p.bias = ep.bias; p.bias_mode = ep.bias ? ep.bias_mode : 0;
@@ -708,8 +945,31 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         return encode_tmap_16bit(m, o.ptr, 3, dims, strides, box);
     };
     for (int i = 0; i < 2; i++) {
-        DOCC_TRY(encode_operand(&maps[i], A[i < n_a ? i : 0], M, uint32_t(bm), p.a_bcast || batch == 1));
-        DOCC_TRY(encode_operand(&maps[2 + i], B[i < n_b ? i : 0], N, uint32_t(bn), p.b_bcast || batch == 1));
+        DOCC_TRY(encode_operand(&maps[i], A[i < n_a ? i : 0], M, use_pair ? 128u : uint32_t(bm), p.a_bcast || batch == 1));
+        DOCC_TRY(encode_operand(&maps[2 + i], B[i < n_b ? i : 0], N, use_pair ? 128u : uint32_t(bn), p.b_bcast || batch == 1));
+    }
+    if (use_pair) {
+        const size_t smem2 = size_t(stages) * ((1 + bn / 256) * 128 * 128) + kStagingBytes + 1024 + 256;
+        if (!g_attr_pair_set[ctx->device & 15]) {
+            DOCC_CUDA_TRY(cudaFuncSetAttribute(tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+            g_attr_pair_set[ctx->device & 15] = true;
+        }
+        const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
+        const int64_t pairs = tiles < ctx->sm_count / 2 ? tiles : ctx->sm_count / 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(unsigned(2 * pairs), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem2;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        DOCC_CUDA_TRY(cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
+        return after_launch(ctx, "tc_gemm_pair_kernel");
     }
 
     const size_t smem = size_t(stages) * (p.a_bytes + p.b_bytes) + kStagingBytes + 1024 + 256;

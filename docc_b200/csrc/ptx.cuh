@@ -69,6 +69,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
+// pulls a tile into L2 without touching shared memory
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
@@ -130,6 +135,56 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Four consecutive 16-deep k-steps of D[tmem] (+)= A[smem] * B[smem] in one asm block: the descriptors advance by
+// `a_step` / `b_step` (address-field units of 16 bytes) per step, only the first step honours `accumulate`.
+// The issuing thread is a single lane, so every scalar instruction between two UMMAs is issue latency the
+// tensor pipe has to cover from its queue; this keeps the k-block down to a dozen instructions.
+// CTAS = 2 issues for a CTA pair (cta_group::2).
+template <int CTAS>
+__device__ __forceinline__ void umma_f16_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                               uint64_t a_step, uint64_t b_step) {
+    if constexpr (CTAS == 1) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            ".reg .b64 ra, rb;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "setp.ne.b32 p, %3, 0;\n"  // the instruction descriptor is never zero: p = true
+            "add.s64 ra, %1, %5;\n"
+            "add.s64 rb, %2, %6;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], ra, rb, %3, p;\n"
+            "add.s64 ra, ra, %5;\n"
+            "add.s64 rb, rb, %6;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], ra, rb, %3, p;\n"
+            "add.s64 ra, ra, %5;\n"
+            "add.s64 rb, rb, %6;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], ra, rb, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_step), "l"(b_step)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            ".reg .b64 ra, rb;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+            "setp.ne.b32 p, %3, 0;\n"
+            "add.s64 ra, %1, %5;\n"
+            "add.s64 rb, %2, %6;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], ra, rb, %3, p;\n"
+            "add.s64 ra, ra, %5;\n"
+            "add.s64 rb, rb, %6;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], ra, rb, %3, p;\n"
+            "add.s64 ra, ra, %5;\n"
+            "add.s64 rb, rb, %6;\n"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], ra, rb, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(a_step), "l"(b_step)
+            : "memory");
+    }
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -185,6 +240,64 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
         : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- CTA pairs (cta_group::2) -----------------------------------------------------------------------
+// Two CTAs of a cluster drive one UMMA with M = 256: each supplies its 128 rows of A and its half of the
+// B tile from its own shared memory and receives its 128 rows of the accumulator in its own tensor
+// memory. One thread of the leader CTA (rank 0) issues the instruction for both.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `smem_addr` (a shared::cta address) in the CTA with rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrive on an mbarrier that may live in the peer CTA (shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion is counted on `cluster_bar`, an mbarrier of
+// either CTA of the pair (no multicast: every CTA loads its own tile)
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t cluster_bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` once all UMMAs issued
+// so far by this thread have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(cta_mask)
+                 : "memory");
+}
 
 // ---- UMMA descriptors -------------------------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle (bits: [0,14) address>>4, [16,30) leading byte

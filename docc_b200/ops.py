@@ -216,6 +216,11 @@ def matmul(A, B, flags=0):
 def linear(X, W, bias=None, act=ACT_NONE, residual=None, alpha=1.0, flags=0):
     """Y = act(alpha * X W^T + bias) + residual with the torch Linear weight layout [out, in]."""
     flags |= _kind(X, W, bias, residual)
+    if bias is not None:
+        # the ABI reads the bias as fp32 for 16-bit operands and in the operand type otherwise
+        want = ord("s") if _prec(X) in (ord("h"), ord("b")) else _prec(X)
+        if _prec(bias) != want:
+            raise TypeError(f"linear: bias must be {'float32' if want == ord('s') else 'float64'} for {chr(_prec(X))!r} operands")
     k = X.shape[-1]
     m = int(np.prod(X.shape[:-1]))
     n = W.shape[0]
