@@ -13,6 +13,7 @@
 // QK^T of block j+1 is issued before P_j V_j, so the tensor pipe computes the next scores while the
 // softmax warps work on the current ones. All waits are bounded.
 #include <cstdlib>
+#include <type_traits>
 
 #include "attention.h"
 #include "device_math.cuh"
@@ -579,6 +580,10 @@ __global__ void __launch_bounds__(320, 1)
             tc_fence_after();
             const bool need_mask = (k0 + kBKV > p.Skv) || (p.causal && k0 + kBKV - 1 > q0[t] + p.causal_off);
             const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;
+            // The block body exists twice, with and without masking: the mask test is uniform over the warp, and as a
+            // run-time condition inside the loops it costs two compare/select instructions per score on every block.
+            auto block_body = [&](auto mask_c) {
+            constexpr bool MASK = decltype(mask_c)::value;
             // Pass 1 (block maximum) with two chunk loads in flight: the next 32 columns are requested
             // before the current ones are reduced, so the TMEM read latency overlaps the arithmetic.
             // four independent running maxima / sums: a single chain of 128 dependent operations would
@@ -586,7 +591,7 @@ __global__ void __launch_bounds__(320, 1)
             float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             uint32_t sa[32], sb[32];
             auto max_chunk = [&](const uint32_t (&sv)[32], int c) {
-                if (need_mask) {
+                if (MASK) {
 #pragma unroll
                     for (int i = 0; i < 32; i++)
                         if (c * 32 + i <= visible) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(sv[i]));
@@ -640,7 +645,7 @@ __global__ void __launch_bounds__(320, 1)
                 for (int i = 0; i < 16; i++) {
                     float x0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_ref));
                     float x1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref));
-                    if (need_mask) {
+                    if (MASK) {
                         if (c * 32 + 2 * i > visible) x0 = 0.f;
                         if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
                     }
@@ -677,6 +682,9 @@ __global__ void __launch_bounds__(320, 1)
                 }
             }
             l += (bl4[0] + bl4[1]) + (bl4[2] + bl4[3]);
+            };
+            if (need_mask) block_body(std::true_type{});
+            else block_body(std::false_type{});
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();

@@ -54,12 +54,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about `ns`
+// nanoseconds have passed, instead of coming back to re-issue the poll (and its loop arithmetic) every few
+// dozen clocks; waiting warps then leave the issue slots and the ALU to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `limit_cycles` SM clocks and returns false. Every spin in the
 // kernels goes through this, so a protocol error ends the kernel with a status code, not a hang.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = 2000000000LL) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_sleep(bar, parity, 20000u)) {
         if (clock64() - t0 > limit_cycles) return false;
     }
     return true;
