@@ -13,6 +13,9 @@
 //   3. the accumulator tile is [oc lanes x pixel columns], i.e. already NCHW: every lane streams its
 //      channel's pixels straight to Y with the bias added.
 // fp32 inputs run three passes (w_lo*x_hi, w_hi*x_lo, w_hi*x_hi) into the same accumulator.
+#include <cstdlib>
+#include <type_traits>
+
 #include "conv.h"
 #include "device_math.cuh"
 #include "gemm_tc.h"
@@ -36,6 +39,7 @@ struct ConvKernelParams {
     int r_max;         // output rows per tile (r_max * Wo <= 256)
     int tiles_m;
     long long total_units;  // tiles_m * N * Ho output-row units
+    int w_stages;  // halo variant: depth of the weight ring
     int tma_out;  // Y rows are 16-byte aligned: full 32-pixel groups go out through TMA stores
     const float* bias;
     float* Y;
@@ -299,61 +303,271 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
-// ---- layout pre-passes ---------------------------------------------------------------------------
-template <typename TIn> __device__ __forceinline__ float ld_f(const TIn* p) { return to_float(*p); }
+// ---- halo variant ---------------------------------------------------------------------------------
+// For images at most 64 - kw + 1 output pixels wide, the tile's input neighbourhood is loaded once and all
+// kh*kw taps read it in place. The halo of a tile of r output rows is (r + kh - 1) input rows of 64 pixel
+// slots (input columns -pad_w .. 63 - pad_w; slots outside the image are zero-filled by TMA), 128 bytes of
+// channels each: one 4-D TMA box per 64-channel block. The accumulator has 64 columns per output row
+// (column = row * 64 + ow, the columns ow >= Wo hold garbage and are never stored); tap (ky, kx) is the
+// same shared-memory tile read from a start address (ky * 64 + kx) * 128 bytes further on, which works
+// because the 128-byte swizzle is a function of the absolute shared-memory address. Against the per-tap
+// loads of the kernel above this cuts the L2 -> SM traffic of the input by kh*kw (weights still stream
+// through their own ring, one 128 x 64 block per tap).
+constexpr int kHaloSlots = 2;
+constexpr int kMaxWStages = 8;  // the weight ring takes what the halo slots leave: its depth has to cover the TMA latency
 
-// X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16. A block moves 64 pixels x 64 channels through shared
-// memory as 32-bit words holding a channel pair: reads walk pixels (coalesced in NCHW), writes walk
-// channels, so every pixel's 64 channels leave as one full 128-byte line. Requires C % 64 == 0.
-template <typename TIn, bool SPLIT>
-__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ X, __nv_bfloat16* __restrict__ hi,
-                                                           __nv_bfloat16* __restrict__ lo, int C, long long HW) {
-    __shared__ uint32_t tile_hi[64][33];
-    __shared__ uint32_t tile_lo[SPLIT ? 64 : 1][33];
-    const long long n = blockIdx.z;
-    const long long p0 = (long long)blockIdx.x * 64;
-    const int c0 = blockIdx.y * 64;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;  // 8 warps
-    const TIn* xin = X + (n * C + c0) * HW;
-    // warp w, iteration i: channel pair cp = w + 8*(i/2), pixel half (i&1)
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int cp = w + 8 * (i >> 1);
-        const int px = (i & 1) * 32 + lane;
-        const long long gp = p0 + px;
-        float a = 0.f, b = 0.f;
-        if (gp < HW) {
-            a = ld_f(xin + (long long)(2 * cp) * HW + gp);
-            b = ld_f(xin + (long long)(2 * cp + 1) * HW + gp);
+constexpr int kHaloThreads = 320;  // TMA warp, UMMA warp, eight epilogue warps (two per tensor-memory lane quadrant)
+
+__global__ void __launch_bounds__(kHaloThreads, 1)
+    conv_halo_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1,
+                     const __grid_constant__ CUtensorMap tmX0, const __grid_constant__ CUtensorMap tmX1,
+                     const __grid_constant__ CUtensorMap tmY, const ConvKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t halo_bytes = uint32_t(p.r_max + p.kh - 1) * 8192u;
+    const uint32_t w_stages = uint32_t(p.w_stages);
+    const uint32_t sH = base;                           // halo slots; reads past a slot's end land in the next region
+    const uint32_t sA = sH + kHaloSlots * halo_bytes;   // weight ring
+    const uint32_t sStage = sA + w_stages * kABytes;    // eight 4 KB staging tiles (one per epilogue warp)
+    const uint32_t bars = sStage + 8 * 4096u;
+    auto full_a = [&](uint32_t i) { return bars + 8u * i; };
+    auto empty_a = [&](uint32_t i) { return bars + 64u + 8u * i; };
+    auto full_h = [&](uint32_t i) { return bars + 128u + 8u * i; };
+    auto empty_h = [&](uint32_t i) { return bars + 144u + 8u * i; };
+    auto tfull_bar = [&](uint32_t i) { return bars + 160u + 8u * i; };
+    auto tempty_bar = [&](uint32_t i) { return bars + 176u + 8u * i; };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 192u - raw_addr));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp == 0 && lane == 0) {
+        for (uint32_t i = 0; i < w_stages; i++) {
+            mbar_init(full_a(i), 1);
+            mbar_init(empty_a(i), 1);
         }
-        const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
-        tile_hi[px][cp] = uint32_t(__bfloat16_as_ushort(ah)) | (uint32_t(__bfloat16_as_ushort(bh)) << 16);
-        if (SPLIT) {
-            const __nv_bfloat16 al = __float2bfloat16_rn(a - __bfloat162float(ah)), bl = __float2bfloat16_rn(b - __bfloat162float(bh));
-            tile_lo[px][cp] = uint32_t(__bfloat16_as_ushort(al)) | (uint32_t(__bfloat16_as_ushort(bl)) << 16);
+        for (uint32_t i = 0; i < 2; i++) {
+            mbar_init(full_h(i), 1);
+            mbar_init(empty_h(i), 1);
+            mbar_init(tfull_bar(i), 1);
+            mbar_init(tempty_bar(i), 8);
         }
+        fence_barrier_init();
+        prefetch_tensormap(&tmW0);
+        prefetch_tensormap(&tmX0);
     }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
     __syncthreads();
-    uint32_t* out_hi = reinterpret_cast<uint32_t*>(hi);
-    uint32_t* out_lo = reinterpret_cast<uint32_t*>(lo);
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int px = w + 8 * i;
-        const long long gp = p0 + px;
-        if (gp < HW) {
-            const long long o = ((n * HW + gp) * C + c0) / 2 + lane;
-            out_hi[o] = tile_hi[px][lane];
-            if (SPLIT) out_lo[o] = tile_lo[px][lane];
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const long long u_begin = p.total_units * blockIdx.x / gridDim.x;
+    const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
+
+    if (warp == 0) {
+        // TMA producer: per (pass, channel block) one halo box, then the kh*kw weight blocks.
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, hs = 0, hph = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            while (ok && next_tile(p, u, u_end, t)) {
+                for (int pass = 0; pass < p.npass && ok; pass++) {
+                    const CUtensorMap* mw = p.pw[pass] ? &tmW1 : &tmW0;
+                    const CUtensorMap* mx = p.px[pass] ? &tmX1 : &tmX0;
+                    for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
+                        if (!mbar_wait(empty_h(hs), hph ^ 1u)) {
+                            conv_timeout(p.status, 25);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(full_h(hs), halo_bytes);
+                        tma_load_4d(sH + hs * halo_bytes, mx, full_h(hs), c0, -p.pad_w, t.oh0 - p.pad_h, t.n);
+                        if (++hs == uint32_t(kHaloSlots)) {
+                            hs = 0;
+                            hph ^= 1u;
+                        }
+                        int k_col = c0;  // column of (tap, channel block) in the re-laid weights: tap * C + c0
+                        for (int tap = 0; tap < p.kh * p.kw; tap++, k_col += p.C) {
+                            if (!mbar_wait(empty_a(s), ph ^ 1u)) {
+                                conv_timeout(p.status, 21);
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_expect_tx(full_a(s), kABytes);
+                            tma_load_2d(sA + s * kABytes, mw, full_a(s), k_col, t.m0);
+                            if (++s == w_stages) {
+                                s = 0;
+                                ph ^= 1u;
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
         }
+    } else if (warp == 1) {
+        // UMMA issuer
+        if (lane == 0) {
+            uint32_t lt = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            const uint64_t a_desc0 = make_smem_desc(sA, 16u, 1024u), h_desc0 = make_smem_desc(sH, 16u, 1024u);
+            const int cblocks = p.npass * (p.C / 64);
+            uint32_t s = 0, ph = 0, hs = 0, hph = 0;
+            uint64_t a_desc = a_desc0;
+            while (ok && next_tile(p, u, u_end, t)) {
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                lt++;
+                if (!mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u)) {
+                    conv_timeout(p.status, 22);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t idesc = make_idesc(128, t.rows * 64, 1, 0, 0);
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int cb = 0; cb < cblocks && ok; cb++) {
+                    if (!mbar_wait(full_h(hs), hph)) {
+                        conv_timeout(p.status, 26);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint64_t row_desc = h_desc0 + uint64_t(hs * (halo_bytes >> 4));
+                    for (int ky = 0; ky < p.kh && ok; ky++, row_desc += (64 * 128) >> 4) {
+                        uint64_t b_desc = row_desc;
+                        for (int kx = 0; kx < p.kw; kx++, b_desc += 128 >> 4) {
+                            if (!mbar_wait(full_a(s), ph)) {
+                                conv_timeout(p.status, 23);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            umma_f16_ss_x4<1>(d_tmem, a_desc, b_desc, idesc, acc, 2, 2);  // +32 bytes per 16-deep k-step
+                            acc = 1;
+                            umma_commit(empty_a(s));
+                            a_desc += kABytes >> 4;
+                            if (++s == w_stages) {
+                                s = 0;
+                                ph ^= 1u;
+                                a_desc = a_desc0;
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(empty_h(hs));
+                    if (++hs == uint32_t(kHaloSlots)) {
+                        hs = 0;
+                        hph ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(buf));
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int wg = (warp - 2) >> 2;
+        uint32_t lt = 0;
+        long long u = u_begin;
+        Tile t;
+        const long long plane = (long long)p.Ho * p.Wo;
+        const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
+        while (next_tile(p, u, u_end, t)) {
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            lt++;
+            if (!mbar_wait(tfull_bar(buf), use & 1u)) {
+                if (lane == 0) conv_timeout(p.status, 24);
+                break;
+            }
+            tc_fence_after();
+            const int oc = t.m0 + q * 32 + lane;
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
+            const bool row_ok = oc < p.c_out;
+            const float bv = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.f;
+            // the two warps of a quadrant take alternate groups of 32 output pixels
+            int gi = 0;
+            for (int rr = 0; rr < t.rows; rr++) {
+                float* yrow = p.Y + ((long long)t.n * p.c_out + (row_ok ? oc : 0)) * plane + (long long)(t.oh0 + rr) * p.Wo;
+                for (int c = 0; c < p.Wo; c += 32, gi++) {
+                    if ((gi & 1) != wg) continue;
+                    const uint32_t col = uint32_t(rr * 64 + c);
+                    if (p.tma_out) {
+                        // a swizzled staging tile of 32 channels x 32 pixels and one TMA store per warp; the tensor map
+                        // clips pixels >= Wo and channels >= C_out
+                        uint32_t r0[16], r1[16];
+                        tmem_ld_x16(t_addr + col, r0);
+                        tmem_ld_x16(t_addr + col + 16u, r1);
+                        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+                        tmem_ld_wait();
+                        __syncwarp();
+#pragma unroll
+                        for (int sub = 0; sub < 2; sub++) {
+                            const uint32_t (&r)[16] = sub ? r1 : r0;
+#pragma unroll
+                            for (int v4 = 0; v4 < 4; v4++) {
+                                const int chunk = sub * 4 + v4;
+                                const uint32_t dst = stage_base + uint32_t(lane) * 128u + uint32_t((chunk ^ (lane & 7)) * 16);
+                                const uint32_t w0 = __float_as_uint(__uint_as_float(r[v4 * 4 + 0]) + bv);
+                                const uint32_t w1 = __float_as_uint(__uint_as_float(r[v4 * 4 + 1]) + bv);
+                                const uint32_t w2 = __float_as_uint(__uint_as_float(r[v4 * 4 + 2]) + bv);
+                                const uint32_t w3 = __float_as_uint(__uint_as_float(r[v4 * 4 + 3]) + bv);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && t.m0 + q * 32 < p.c_out) {
+                            tma_store_4d(&tmY, stage_base, c, t.oh0 + rr, t.m0 + q * 32, t.n);
+                            tma_store_commit();
+                        }
+                    } else {
+#pragma unroll
+                        for (int sub = 0; sub < 2; sub++) {
+                            uint32_t r[16];
+                            tmem_ld_x16(t_addr + col + uint32_t(sub * 16), r);
+                            tmem_ld_wait();
+                            if (!row_ok) continue;
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (c + sub * 16 + j < p.Wo) yrow[c + sub * 16 + j] = __uint_as_float(r[j]) + bv;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+        if (p.tma_out && lane == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
-// W [oc][c][taps] -> hi (and lo) [oc][taps][c]
+// ---- layout pre-passes ---------------------------------------------------------------------------
+template <typename TIn> __device__ __forceinline__ float ld_f(const TIn* p) { return to_float(*p); }
+
+// W [oc][c][taps] -> hi (and lo) [oc][taps][c]; `part` of `parts` cooperating blocks
 template <typename TIn, bool SPLIT>
-__global__ void __launch_bounds__(256) weight_relayout_kernel(const TIn* __restrict__ Wt, __nv_bfloat16* __restrict__ hi,
-                                                              __nv_bfloat16* __restrict__ lo, int c_out, int C, int taps) {
+__device__ __forceinline__ void weight_relayout(const TIn* __restrict__ Wt, __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                                int c_out, int C, int taps, long long part, long long parts) {
     const long long total = (long long)c_out * C * taps;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    for (long long i = part * blockDim.x + threadIdx.x; i < total; i += parts * blockDim.x) {
         const int c = int(i % C);
         const int tap = int((i / C) % taps);
         const long long oc = i / ((long long)C * taps);
@@ -364,7 +578,87 @@ __global__ void __launch_bounds__(256) weight_relayout_kernel(const TIn* __restr
     }
 }
 
+// X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16, and the weights in the same launch (the blocks of the last
+// grid row, blockIdx.y == C / 64). A block moves PX pixels x 64 channels through shared memory as 32-bit
+// words holding a channel pair: reads walk pixels (coalesced in NCHW), writes walk channels, so every
+// pixel's 64 channels leave as one full 128-byte line. Requires C % 64 == 0.
+// PAIR (16-bit input, HW even): every lane reads two neighbouring pixels as one 32-bit word and a block moves
+// 128 pixels; otherwise one element per load and 64 pixels.
+template <typename TIn, bool SPLIT, bool PAIR>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ X, __nv_bfloat16* __restrict__ hi,
+                                                           __nv_bfloat16* __restrict__ lo, int C, long long HW, const TIn* __restrict__ Wt,
+                                                           __nv_bfloat16* __restrict__ w_hi, __nv_bfloat16* __restrict__ w_lo, int c_out, int taps) {
+    constexpr int PX = PAIR ? 128 : 64;
+    __shared__ uint32_t tile_hi[PX][33];
+    __shared__ uint32_t tile_lo[SPLIT ? PX : 1][33];
+    if (blockIdx.y == gridDim.y - 1) {
+        weight_relayout<TIn, SPLIT>(Wt, w_hi, w_lo, c_out, C, taps, (long long)blockIdx.z * gridDim.x + blockIdx.x, (long long)gridDim.x * gridDim.z);
+        return;
+    }
+    const long long n = blockIdx.z;
+    const long long p0 = (long long)blockIdx.x * PX;
+    const int c0 = blockIdx.y * 64;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;  // 8 warps
+    const TIn* xin = X + (n * C + c0) * HW;
+    if constexpr (PAIR) {
+        static_assert(sizeof(TIn) == 2 && !SPLIT, "pixel pairs are read as 32-bit words of a 16-bit type");
+        // warp w, iteration i: channel pair cp = w + 8*(i/2), pixels 64*(i&1) + 2*lane, +1
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int cp = w + 8 * (i >> 1);
+            const int px = (i & 1) * 64 + 2 * lane;
+            const long long gp = p0 + px;
+            uint32_t a = 0, b = 0;  // (pixel px, pixel px + 1) of channels 2cp and 2cp + 1
+            if (gp < HW) {          // HW and gp are even: the pair is inside or outside as a whole
+                a = *reinterpret_cast<const uint32_t*>(xin + (long long)(2 * cp) * HW + gp);
+                b = *reinterpret_cast<const uint32_t*>(xin + (long long)(2 * cp + 1) * HW + gp);
+            }
+            if constexpr (!std::is_same<TIn, __nv_bfloat16>::value) {  // fp16 -> bf16
+                const __half2 ha = *reinterpret_cast<const __half2*>(&a), hb = *reinterpret_cast<const __half2*>(&b);
+                const __nv_bfloat162 ba = __float22bfloat162_rn(__half22float2(ha)), bb = __float22bfloat162_rn(__half22float2(hb));
+                a = *reinterpret_cast<const uint32_t*>(&ba);
+                b = *reinterpret_cast<const uint32_t*>(&bb);
+            }
+            tile_hi[px][cp] = __byte_perm(a, b, 0x5410);
+            tile_hi[px + 1][cp] = __byte_perm(a, b, 0x7632);
+        }
+    } else {
+        // warp w, iteration i: channel pair cp = w + 8*(i/2), pixel half (i&1)
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int cp = w + 8 * (i >> 1);
+            const int px = (i & 1) * 32 + lane;
+            const long long gp = p0 + px;
+            float a = 0.f, b = 0.f;
+            if (gp < HW) {
+                a = ld_f(xin + (long long)(2 * cp) * HW + gp);
+                b = ld_f(xin + (long long)(2 * cp + 1) * HW + gp);
+            }
+            const __nv_bfloat16 ah = __float2bfloat16_rn(a), bh = __float2bfloat16_rn(b);
+            tile_hi[px][cp] = uint32_t(__bfloat16_as_ushort(ah)) | (uint32_t(__bfloat16_as_ushort(bh)) << 16);
+            if (SPLIT) {
+                const __nv_bfloat16 al = __float2bfloat16_rn(a - __bfloat162float(ah)), bl = __float2bfloat16_rn(b - __bfloat162float(bh));
+                tile_lo[px][cp] = uint32_t(__bfloat16_as_ushort(al)) | (uint32_t(__bfloat16_as_ushort(bl)) << 16);
+            }
+        }
+    }
+    __syncthreads();
+    uint32_t* out_hi = reinterpret_cast<uint32_t*>(hi);
+    uint32_t* out_lo = reinterpret_cast<uint32_t*>(lo);
+#pragma unroll
+    for (int i = 0; i < PX / 8; i++) {
+        const int px = w + 8 * i;
+        const long long gp = p0 + px;
+        if (gp < HW) {
+            const long long o = ((n * HW + gp) * C + c0) / 2 + lane;
+            out_hi[o] = tile_hi[px][lane];
+            if (SPLIT) out_lo[o] = tile_lo[px][lane];
+        }
+    }
+}
+
 bool g_conv_attr[16] = {false};
+bool g_halo_attr[16] = {false};
 
 }  // namespace
 
@@ -386,22 +680,36 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     __nv_bfloat16* w_lo = w_hi + (w_elems + 63) / 64 * 64;
 
     {
-        dim3 grid(unsigned(ceil_div(HW, 64)), unsigned(q.C / 64), unsigned(q.N));
+        // one launch re-lays the input and (in the extra grid row) the weights
+        const bool pair = !split && HW % 2 == 0 && reinterpret_cast<uintptr_t>(X) % 4 == 0;
+        dim3 grid(unsigned(ceil_div(HW, pair ? 128 : 64)), unsigned(q.C / 64 + 1), unsigned(q.N));
         if (grid.z > 65535) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: batch too large");
-        if (split) nchw_to_nhwc_kernel<float, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW);
-        else nchw_to_nhwc_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW);
+        if (split)
+            nchw_to_nhwc_kernel<float, true, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                  static_cast<const float*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
+        else if (pair)
+            nchw_to_nhwc_kernel<__nv_bfloat16, false, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                          static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
+        else
+            nchw_to_nhwc_kernel<__nv_bfloat16, false, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                           static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
         DOCC_TRY(after_launch(ctx, "nchw_to_nhwc_kernel"));
-        int64_t blocks = ceil_div(int64_t(w_elems), 256);
-        if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-        if (split) weight_relayout_kernel<float, true><<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(Wt), w_hi, w_lo, int(q.c_out), int(q.C), int(taps));
-        else weight_relayout_kernel<__nv_bfloat16, false><<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(q.C), int(taps));
-        DOCC_TRY(after_launch(ctx, "weight_relayout_kernel"));
     }
+
+    // narrow images: the halo variant loads each tile's input neighbourhood once for all taps
+    int halo_rmax = int(10 - q.kh) < 4 ? int(10 - q.kh) : 4;  // r + kh - 1 <= 9 halo rows of 8 KB per slot (two slots, three weight stages)
+    static const int halo_mode = [] { const char* e = getenv("DOCC_B200_CONV_HALO"); return e ? atoi(e) : 1; }();
+    const bool halo = halo_mode && q.Wo + q.kw - 1 <= 64 && halo_rmax >= 1;
 
     CUtensorMap maps[5];
     memset(maps, 0, sizeof(maps));
     const bool tma_out = q.Wo % 4 == 0 && reinterpret_cast<uintptr_t>(Y) % 16 == 0;
-    if (tma_out) {
+    if (tma_out && halo) {
+        const uint64_t yd[4] = {uint64_t(q.Wo), uint64_t(q.Ho), uint64_t(q.c_out), uint64_t(q.N)};
+        const uint64_t ys[3] = {uint64_t(q.Wo) * 4, uint64_t(q.Ho * q.Wo) * 4, uint64_t(q.Ho * q.Wo) * q.c_out * 4};
+        const uint32_t yb[4] = {32, 1, 32, 1};
+        DOCC_TRY(encode_tmap(&maps[4], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, CU_TENSOR_MAP_SWIZZLE_128B, Y, 4, yd, ys, yb));
+    } else if (tma_out) {
         const uint64_t yd[3] = {uint64_t(q.Ho * q.Wo), uint64_t(q.c_out), uint64_t(q.N)};
         const uint64_t ys[2] = {uint64_t(q.Ho * q.Wo) * 4, uint64_t(q.Ho * q.Wo) * q.c_out * 4};
         const uint32_t yb[3] = {32, 32, 1};
@@ -416,7 +724,7 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
         DOCC_TRY(encode_tmap_16bit(&maps[i], wp, 2, wd, ws, wb));
         const uint64_t xd[4] = {uint64_t(q.C), uint64_t(q.W), uint64_t(q.H), uint64_t(q.N)};
         const uint64_t xs[3] = {uint64_t(q.C) * 2, uint64_t(q.W) * q.C * 2, uint64_t(HW) * q.C * 2};
-        const uint32_t xb[4] = {64, uint32_t(q.Wo), 1, 1};
+        const uint32_t xb[4] = {64, halo ? 64u : uint32_t(q.Wo), halo ? uint32_t(halo_rmax + q.kh - 1) : 1u, 1};
         DOCC_TRY(encode_tmap_16bit(&maps[2 + i], xp, 4, xd, xs, xb));
     }
 
@@ -434,11 +742,28 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     }
     p.r_max = int(256 / q.Wo);
     if (p.r_max > 8) p.r_max = 8;
+    if (halo) p.r_max = halo_rmax;
     p.tiles_m = int(ceil_div(q.c_out, 128));
     p.total_units = (long long)p.tiles_m * q.N * q.Ho;
     p.tma_out = tma_out ? 1 : 0;
     p.bias = bias; p.Y = Y; p.status = ctx->status_dev;
 
+    if (halo) {
+        const size_t halo_total = size_t(kHaloSlots) * size_t(p.r_max + p.kh - 1) * 8192;
+        const size_t fixed = 8 * 4096 + 1024 + 256;
+        int w_stages = int((227 * 1024 - halo_total - fixed) / kABytes);
+        if (w_stages > kMaxWStages) w_stages = kMaxWStages;
+        p.w_stages = w_stages;
+        const size_t smem_h = halo_total + size_t(w_stages) * kABytes + fixed;
+        if (!g_halo_attr[ctx->device & 15]) {
+            DOCC_CUDA_TRY(cudaFuncSetAttribute(conv_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            g_halo_attr[ctx->device & 15] = true;
+        }
+        long long grid_h = ceil_div(p.total_units, p.r_max);
+        if (grid_h > ctx->sm_count) grid_h = ctx->sm_count;
+        conv_halo_kernel<<<unsigned(grid_h), kHaloThreads, smem_h, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+        return after_launch(ctx, "conv_halo_kernel");
+    }
     const size_t smem = size_t(kStages) * (kABytes + kBBytes) + 4 * 4096 + 1024 + 256;
     if (!g_conv_attr[ctx->device & 15]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
