@@ -243,6 +243,34 @@ def test_conv_config3_shape_reduced_batch(rt):
     assert relerr(got16, ref16) <= TOL_16
 
 
+# Tensor-core convolution geometries (C_in a multiple of 64): narrow images take the kernel that loads each
+# tile's input neighbourhood once (ragged widths, partial channel tiles, 1x1 to 7x7 filters, two channel
+# blocks), images wider than 62 output pixels the per-tap kernel.
+@pytest.mark.parametrize("n,c,h,w,co,k,pad", [
+    (2, 64, 20, 30, 96, 3, 1),    # rows not a multiple of 16 bytes: direct stores; C_out below one tile
+    (1, 128, 9, 62, 130, 3, 1),   # widest narrow case, two channel blocks, second channel tile nearly empty
+    (1, 64, 40, 80, 64, 3, 1),    # wide image
+    (2, 64, 12, 12, 32, 5, 2),
+    (1, 64, 16, 16, 64, 1, 0),
+    (1, 64, 10, 24, 64, 7, 3),
+    (1, 64, 7, 7, 128, 3, 0),     # no padding, output 5x5
+])
+def test_conv_tensor_core_geometries(rt, n, c, h, w, co, k, pad):
+    torch.manual_seed(7)
+    x = torch.randn(n, c, h, w)
+    wt = torch.randn(co, c, k, k) / (c * k * k) ** 0.5
+    b = torch.randn(co)
+    pads = [pad, pad, pad, pad]
+    ref = oracle.conv(x.numpy(), wt.numpy(), b.numpy(), pads=pads)
+    got = host(ops.conv(x.cuda(), wt.cuda(), b.cuda(), pads=pads))
+    assert got.shape == ref.shape
+    assert relerr(got, ref) <= TOL_F32
+    xb, wb = x.bfloat16(), wt.bfloat16()
+    ref16 = oracle.conv(xb.float().numpy(), wb.float().numpy(), b.numpy(), pads=pads)
+    got16 = host(ops.conv(xb.cuda(), wb.cuda(), b.cuda(), pads=pads))
+    assert relerr(got16, ref16) <= TOL_16
+
+
 def test_conv_linearity_full_config3(rt):
     # size-independent property at the full config: conv(x1 + x2) == conv(x1) + conv(x2)
     torch.manual_seed(2)
