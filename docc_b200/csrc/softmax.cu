@@ -6,6 +6,8 @@
 // and written once: 2 * rows * cols * sizeof(T) bytes of HBM traffic.
 #include <cfloat>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "device_math.cuh"
 
@@ -300,7 +302,10 @@ int launch_rows(Ctx* ctx, const T* X, T* Y, int64_t rows, int64_t cols) {
     constexpr int BLOCK = TPR > 256 ? TPR : 256;
     constexpr int RPB = BLOCK / TPR;
     const int64_t groups = ceil_div(rows, RPB);
-    const int64_t max_blocks = int64_t(ctx->sm_count) * (2048 / BLOCK);
+    // One row group per block: the hardware block scheduler then balances the SMs dynamically. A grid capped at the
+    // resident block count (grid-stride inside the kernel) left part of the SMs idle during the last, partly filled
+    // round of groups (5740 -> 5920 GB/s on fp32 [8192,4096]).
+    const int64_t max_blocks = 0x7fffffff;
     const int grid = int(groups < max_blocks ? groups : max_blocks);
     softmax_rows_kernel<T, VEC, VPT, TPR, BLOCK><<<grid, BLOCK, 0, ctx->stream>>>(X, Y, rows, cols);
     return after_launch(ctx, "softmax_rows_kernel");
@@ -315,7 +320,7 @@ int dispatch_rows(Ctx* ctx, const T* X, T* Y, int64_t rows, int64_t cols, bool* 
     if (packs <= 128) return launch_rows<T, VEC, 4, 32>(ctx, X, Y, rows, cols);
     if (packs <= 256) return launch_rows<T, VEC, 8, 32>(ctx, X, Y, rows, cols);
     if (packs <= 512) return launch_rows<T, VEC, 4, 128>(ctx, X, Y, rows, cols);
-    if (packs <= 1024) return launch_rows<T, VEC, 8, 128>(ctx, X, Y, rows, cols);
+    if (packs <= 1024) return launch_rows<T, VEC, 4, 256>(ctx, X, Y, rows, cols);  // 16 values per thread instead of 32: more resident blocks
     if (packs <= 2048) return launch_rows<T, VEC, 8, 256>(ctx, X, Y, rows, cols);
     if (packs <= 8192) return launch_rows<T, VEC, 8, 1024>(ctx, X, Y, rows, cols);
     *handled = false;
