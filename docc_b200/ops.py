@@ -197,6 +197,20 @@ def gemm(A, B, C=None, alpha=1.0, beta=0.0, transa=False, transb=False, layout=R
     return C
 
 
+def gemm_strided(precision, layout, transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, flags=0):
+    """GEMM on flat buffers with explicit leading dimensions, the form docc's generated code passes to BLAS
+    (gemm_node.cpp:441-520): ``C`` is updated in place. ``precision`` is one of 'h', 's', 'd', 'b'."""
+    flags |= _kind(A, B, C)
+    prec = ord(precision)
+    if prec != _prec(A) or prec != _prec(B) or prec != _prec(C):
+        raise TypeError(f"gemm_strided: operands are not all of precision {precision!r}")
+    al, be = _scalar(prec, float(alpha)), _scalar(prec, float(beta))
+    call("docc_b200_gemm", prec, int(layout), TRANS if transa else NO_TRANS, TRANS if transb else NO_TRANS, int(m), int(n), int(k),
+         ctypes.cast(ctypes.pointer(al), _vp), _ptr(A), int(lda), _ptr(B), int(ldb),
+         ctypes.cast(ctypes.pointer(be), _vp), _ptr(C), int(ldc), flags)
+    return C
+
+
 def matmul(A, B, flags=0):
     """Batched row-major matmul with numpy broadcasting rules on the batch dims (MatMulNode)."""
     flags |= _kind(A, B)
