@@ -127,7 +127,9 @@ template <typename T, int VPT, int TPR>
 int launch_ln(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
     constexpr int BLOCK = TPR > 256 ? TPR : 256;
     const int64_t groups = ceil_div(rows, BLOCK / TPR);
-    const int64_t cap = int64_t(ctx->sm_count) * (2048 / BLOCK);
+    // one row group per block (the block scheduler balances the SMs; a resident-size grid with a stride loop leaves SMs
+    // idle in the last partial round of groups)
+    const int64_t cap = 0x7fffffff;
     layernorm_kernel<T, VPT, TPR, BLOCK><<<int(groups < cap ? groups : cap), BLOCK, 0, ctx->stream>>>(X, g, b, eps, Y, rows, cols);
     return after_launch(ctx, "layernorm_kernel");
 }
