@@ -128,6 +128,42 @@ def test_gemm_bf16(rt):
     assert relerr(got_t, ref) <= TOL_16
 
 
+# Problems large enough for the CTA-pair kernel (K-major operands, at least 74 tiles of 256x256): ragged M and N,
+# the 256x512 tile of a long K, fp32 as three passes, and the fused epilogue. The reference is torch in fp64 on the
+# GPU (the oracle's scalar loops would take minutes at these sizes); a row block is also checked against the oracle.
+@pytest.mark.parametrize("m,n,k", [(2500, 2700, 1000), (2560, 2048, 512), (4096, 4352, 4096)])
+def test_gemm_bf16_cta_pair_paths(rt, m, n, k):
+    torch.manual_seed(21)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    bt = torch.randn(n, k, device="cuda").bfloat16()
+    got = ops.gemm(a, bt, transb=True)
+    ops.sync()
+    ref = a.double() @ bt.double().t()
+    assert ((got.double() - ref).abs().max() / ref.abs().max()).item() <= TOL_16
+    sub = oracle.gemm(a[-8:].float().cpu().numpy(), bt.float().cpu().numpy(), transb=True)
+    assert relerr(got[-8:].float().cpu().numpy(), sub) <= TOL_16
+
+
+def test_gemm_fp32_and_linear_cta_pair_paths(rt):
+    torch.manual_seed(22)
+    a = torch.randn(2304, 1536, device="cuda")
+    bt = torch.randn(2816, 1536, device="cuda")
+    got = ops.gemm(a, bt, transb=True)
+    ops.sync()
+    ref = a.double() @ bt.double().t()
+    assert ((got.double() - ref).abs().max() / ref.abs().max()).item() <= TOL_F32
+    x = torch.randn(2048, 1024, device="cuda").bfloat16()
+    w = torch.randn(2560, 1024, device="cuda").bfloat16() / 32
+    bias = torch.randn(2560, device="cuda")
+    res = torch.randn(2048, 2560, device="cuda").bfloat16()
+    y = ops.linear(x, w, bias, ops.ACT_GELU_ERF, res)
+    ops.sync()
+    ref = torch.nn.functional.gelu(x.double() @ w.double().t() + bias.double()) + res.double()
+    assert ((y.double() - ref).abs().max() / ref.abs().max()).item() <= TOL_16
+    with pytest.raises(TypeError):
+        ops.linear(x, w, bias.bfloat16())  # the ABI reads the bias of a 16-bit layer as fp32
+
+
 def test_gemm_beta_zero_ignores_nan_in_c(rt):
     a = torch.ones(70, 70, device="cuda", dtype=torch.float64)
     c = torch.full((70, 70), float("nan"), device="cuda", dtype=torch.float64)
