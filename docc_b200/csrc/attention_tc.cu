@@ -32,6 +32,7 @@ constexpr int kAttnThreads = 192;
 struct AttnKernelParams {
     int Sq, Skv, H;
     int n_qtiles;
+    int n_items;  // persistent kernel: (batch, head, tile pair) work items
     int causal;
     int causal_off;  // Skv - Sq: query i sees keys j <= i + causal_off
     float scale_log2;  // scale * log2(e)
@@ -745,6 +746,423 @@ __global__ void __launch_bounds__(320, 1)
     }
 }
 
+template <int D, bool IS_BF16, bool SPLIT>
+__global__ void __launch_bounds__(320, 1)
+    attention_tc2p_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmQl,
+                         const __grid_constant__ CUtensorMap tmKl, const __grid_constant__ CUtensorMap tmVl,
+                         const AttnKernelParams p) {
+    constexpr int DC = D / 64;
+    constexpr uint32_t kTile = uint32_t(DC) * 16384u;
+    constexpr int QP = SPLIT ? 2 : 1;  // planes per query tile
+    constexpr int EB = SPLIT ? 4 : 2;  // ring entries per key block: K_hi, [K_lo], V_hi, [V_lo]
+    constexpr int NS = attn2_slots(D, SPLIT);
+    constexpr uint32_t kTmemCols = 512;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t sQ = base;                      // two query tiles (x hi/lo planes): tile t plane pl at (t*QP + pl)*kTile
+    const uint32_t sKV = sQ + 2 * QP * kTile;      // NS ring slots
+    const uint32_t bars = sKV + uint32_t(NS) * kTile;
+    auto kv_full = [&](int i) { return bars + 8u * uint32_t(i); };
+    auto kv_empty = [&](int i) { return bars + 64u + 8u * uint32_t(i); };
+    auto q_full = [&](int t) { return bars + 128u + 8u * uint32_t(t); };
+    auto s_full = [&](int t) { return bars + 144u + 8u * uint32_t(t); };
+    auto p_full = [&](int t) { return bars + 160u + 8u * uint32_t(t); };
+    auto o_full = [&](int t) { return bars + 176u + 8u * uint32_t(t); };
+    auto q_empty = [&](int t) { return bars + 192u + 8u * uint32_t(t); };  // issuer -> producer: Q_t may be overwritten
+    auto o_empty = [&](int t) { return bars + 208u + 8u * uint32_t(t); };  // softmax group -> issuer: O_t has been stored
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 224u - raw_addr));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_pairs = (p.n_qtiles + 1) / 2;
+    // work item = (batch, head, pair of query tiles); a CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...
+    int q0[2], nb[2], n_max = 0, h = 0, b = 0;
+    auto set_item = [&](int item) {
+        const int pair = item % n_pairs;
+        const int bh = item / n_pairs;
+        h = bh % p.H;
+        b = bh / p.H;
+        for (int t = 0; t < 2; t++) {
+            q0[t] = (pair * 2 + t) * kBQ;
+            nb[t] = q0[t] < p.Sq ? (p.Skv + kBKV - 1) / kBKV : 0;  // not used with a causal mask
+        }
+        n_max = nb[0] > nb[1] ? nb[0] : nb[1];
+    };
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < NS; i++) {
+            mbar_init(kv_full(i), 1);
+            mbar_init(kv_empty(i), 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(q_full(t), 1);
+            mbar_init(s_full(t), 1);
+            mbar_init(p_full(t), 4);
+            mbar_init(o_full(t), 1);
+            mbar_init(q_empty(t), 1);
+            mbar_init(o_empty(t), 4);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+          uint32_t ring = 0;          // ring entries issued so far (the ring runs on across items)
+          uint32_t q_use[2] = {0, 0};  // items in which tile t was active so far
+          bool alive = true;
+          for (int item = blockIdx.x; item < p.n_items && alive; item += gridDim.x) {
+            set_item(item);
+            for (int t = 0; t < 2; t++) {
+                if (nb[t] == 0) continue;
+                // the previous item's last Q K^T of this tile has read the old Q_t
+                if (!mbar_wait(q_empty(t), (q_use[t] & 1u) ^ 1u)) { attn_timeout(p.status, 38); alive = false; break; }
+                q_use[t]++;
+                mbar_arrive_expect_tx(q_full(t), QP * kTile);
+                for (int pl = 0; pl < QP; pl++)
+                    for (int c = 0; c < DC; c++)
+                        tma_load_4d(sQ + uint32_t(t * QP + pl) * kTile + uint32_t(c) * 16384u, pl ? &tmQl : &tmQ, q_full(t), c * 64, q0[t], h, b);
+            }
+            for (int i = 0; i < EB * n_max && alive; i++, ring++) {  // entry e = i % EB of block j = i / EB
+                const int s = int(ring % uint32_t(NS));
+                const uint32_t ph = (ring / uint32_t(NS)) & 1u;
+                if (!mbar_wait(kv_empty(s), ph ^ 1u)) { attn_timeout(p.status, 31); alive = false; break; }
+                mbar_arrive_expect_tx(kv_full(s), kTile);
+                const int e = i % EB;
+                const CUtensorMap* m = SPLIT ? (e == 0 ? &tmK : e == 1 ? &tmKl : e == 2 ? &tmV : &tmVl) : (e ? &tmV : &tmK);
+                for (int c = 0; c < DC; c++)
+                    tma_load_4d(sKV + uint32_t(s) * kTile + uint32_t(c) * 16384u, m, kv_full(s), c * 64, (i / EB) * kBKV, h, b);
+            }
+          }
+        }
+    } else if (warp == 1) {
+        // ---------------- UMMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc(kBQ, kBKV, IS_BF16 ? 1 : 0, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc(kBQ, D, IS_BF16 ? 1 : 0, 0, 1);
+            bool ok = true;
+            uint32_t ring_base = 0;                        // ring entries consumed by earlier items
+            uint32_t q_use[2] = {0, 0}, p_cnt[2] = {0, 0};  // items with tile t active / P_t blocks consumed so far
+            auto slot_of = [&](int i) { return int((ring_base + uint32_t(i)) % uint32_t(NS)); };
+            auto wait_slot = [&](int i) -> uint32_t {  // returns the slot base, 0 on timeout
+                const uint32_t g = ring_base + uint32_t(i);
+                const int s = int(g % uint32_t(NS));
+                if (!mbar_wait(kv_full(s), (g / uint32_t(NS)) & 1u)) { attn_timeout(p.status, 32); ok = false; return 0u; }
+                tc_fence_after();
+                return sKV + uint32_t(s) * kTile;
+            };
+            // Q K^T of tile t: hi*hi, plus the two cross terms for fp32 operands (small terms first)
+            // Descriptors are built once per operand tile; the k-steps only add a constant to the address
+            // field (16-byte units), which keeps the issuing thread ahead of the tensor pipe.
+            auto issue_qk = [&](int t, uint32_t kb_hi, uint32_t kb_lo) {
+                const uint32_t d_tmem = tmem_base + uint32_t(t) * 128u;
+                const uint64_t q_hi = make_smem_desc(sQ + uint32_t(t * QP) * kTile, 16u, 1024u);
+                const uint64_t q_lo = q_hi + uint64_t(kTile >> 4);
+                uint32_t acc = 0;
+                auto product = [&](uint64_t qd, uint32_t kb) {
+                    const uint64_t kd = make_smem_desc(kb, 16u, 1024u);
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint64_t off = uint64_t((uint32_t(kk / 4) * 16384u + uint32_t(kk % 4) * 32u) >> 4);
+                        umma_f16_ss(d_tmem, qd + off, kd + off, idesc_qk, acc);
+                        acc = 1;
+                    }
+                };
+                if (SPLIT) {
+                    product(q_lo, kb_hi);
+                    product(q_hi, kb_lo);
+                }
+                product(q_hi, kb_hi);
+                umma_commit(s_full(t));
+            };
+          for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+            set_item(item);
+            for (int t = 0; t < 2 && ok; t++) {
+                if (nb[t] == 0) continue;
+                if (!mbar_wait(q_full(t), q_use[t] & 1u)) { attn_timeout(p.status, 33); ok = false; }
+            }
+            if (ok) {
+                const uint32_t k_hi = wait_slot(0);
+                const uint32_t k_lo = (SPLIT && ok) ? wait_slot(1) : 0u;
+                if (ok) {
+                    for (int t = 0; t < 2; t++) {
+                        if (nb[t] == 0) continue;
+                        issue_qk(t, k_hi, k_lo);
+                        if (nb[t] == 1) umma_commit(q_empty(t));  // that was this item's last read of Q_t
+                    }
+                    umma_commit(kv_empty(slot_of(0)));
+                    if (SPLIT) umma_commit(kv_empty(slot_of(1)));
+                }
+            }
+            for (int j = 0; j < n_max && ok; j++) {
+                const int iv = EB * j + (SPLIT ? 2 : 1);      // first V entry of block j
+                const int ik = EB * (j + 1);                  // first K entry of block j+1
+                const uint32_t v_hi = wait_slot(iv);
+                if (!ok) break;
+                const uint32_t v_lo = SPLIT ? wait_slot(iv + 1) : 0u;
+                if (!ok) break;
+                uint32_t k_hi = 0, k_lo = 0;
+                if (j + 1 < n_max) {
+                    k_hi = wait_slot(ik);
+                    if (!ok) break;
+                    if (SPLIT) k_lo = wait_slot(ik + 1);
+                    if (!ok) break;
+                }
+                for (int t = 0; t < 2 && ok; t++) {
+                    if (j >= nb[t]) continue;
+                    // the previous item's O_t must have left tensor memory before this item's first P V overwrites it
+                    if (j == 0 && !mbar_wait(o_empty(t), (q_use[t] & 1u) ^ 1u)) { attn_timeout(p.status, 39); ok = false; break; }
+                    if (!mbar_wait(p_full(t), p_cnt[t] & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
+                    p_cnt[t]++;
+                    tc_fence_after();
+                    const uint32_t o_tmem = tmem_base + 256u + uint32_t(t) * 128u;
+                    const uint32_t p_hi = tmem_base + uint32_t(t) * 128u;  // P_t over the first 64 columns of S_t
+                    const uint32_t p_lo = p_hi + 64u;                       // (fp32 path) low part over the last 64
+                    uint32_t acc = j > 0 ? 1u : 0u;
+                    auto product = [&](uint32_t pa, uint32_t vb) {
+                        const uint64_t vd = make_smem_desc(vb, 16384u, 1024u);
+#pragma unroll
+                        for (int kk = 0; kk < kBKV / 16; kk++) {
+                            umma_f16_ts(o_tmem, pa + uint32_t(kk) * 8u, vd + uint64_t(kk * (2048 / 16)), idesc_pv, acc);
+                            acc = 1;
+                        }
+                    };
+                    if (SPLIT) {
+                        product(p_lo, v_hi);
+                        product(p_hi, v_lo);
+                    }
+                    product(p_hi, v_hi);
+                    umma_commit(o_full(t));
+                    if (j + 1 < nb[t]) {
+                        issue_qk(t, k_hi, k_lo);
+                        if (j + 2 == nb[t]) umma_commit(q_empty(t));
+                    }
+                }
+                if (!ok) break;
+                umma_commit(kv_empty(slot_of(iv)));
+                if (SPLIT) umma_commit(kv_empty(slot_of(iv + 1)));
+                if (j + 1 < n_max) {
+                    umma_commit(kv_empty(slot_of(ik)));
+                    if (SPLIT) umma_commit(kv_empty(slot_of(ik + 1)));
+                }
+            }
+            ring_base += uint32_t(EB * n_max);
+            for (int t = 0; t < 2; t++) if (nb[t] > 0) q_use[t]++;
+          }
+        }
+    } else {
+        // ---------------- softmax groups ----------------
+        const int t = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
+        const uint32_t s_addr = lane_addr + uint32_t(t) * 128u;
+        const uint32_t o_addr = lane_addr + 256u + uint32_t(t) * 128u;
+        bool ok = true;
+        uint32_t s_cnt = 0, o_cnt = 0;  // score blocks consumed / P V products awaited so far (all items)
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        set_item(item);
+        const int row = q0[t] + r;
+        const int n_t = nb[t];
+        if (n_t == 0) continue;  // odd tile count: the second tile of the last pair does not exist
+        float m = -INFINITY;  // maximum the stored exponentials are relative to
+        float l = 0.f;
+        const int row_limit = p.Skv - 1;
+
+        for (int j = 0; j < n_t && ok; j++) {
+            const int k0 = j * kBKV;
+            if (!mbar_wait(s_full(t), s_cnt & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 35);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            s_cnt++;
+            const bool need_mask = k0 + kBKV > p.Skv;
+            const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;
+            // The block body exists twice, with and without masking: the mask test is uniform over the warp, and as a
+            // run-time condition inside the loops it costs two compare/select instructions per score on every block.
+            auto block_body = [&](auto mask_c) {
+            constexpr bool MASK = decltype(mask_c)::value;
+            // Pass 1 (block maximum) with two chunk loads in flight: the next 32 columns are requested
+            // before the current ones are reduced, so the TMEM read latency overlaps the arithmetic.
+            // four independent running maxima / sums: a single chain of 128 dependent operations would
+            // leave the two warps per scheduler waiting on arithmetic latency
+            float bm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            uint32_t sa[32], sb[32];
+            auto max_chunk = [&](const uint32_t (&sv)[32], int c) {
+                if (MASK) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i <= visible) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(sv[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) bm4[i & 3] = fmaxf(bm4[i & 3], __uint_as_float(sv[i]));
+                }
+            };
+            tmem_ld_x32(s_addr, sa);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 32u, sb);
+            max_chunk(sa, 0);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 64u, sa);
+            max_chunk(sb, 1);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 96u, sb);
+            max_chunk(sa, 2);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr, sa);  // first chunk of pass 2
+            max_chunk(sb, 3);
+            const float bm = fmaxf(fmaxf(bm4[0], bm4[1]), fmaxf(bm4[2], bm4[3]));
+            const float m_cand = fmaxf(m, bm * p.scale_log2);
+            // raise the reference maximum only when it moved by more than 8 (a factor 256 of headroom)
+            const bool raise = m_cand > m + 8.0f;  // also true on the first block (m = -inf) when any key is visible
+            if (__any_sync(0xffffffffu, raise)) {
+                const float m_new = raise ? m_cand : m;
+                const float f = raise ? ex2(m - m_new) : 1.0f;  // 0 when m = -inf
+                if (j > 0) {
+                    // S_t of this block is complete, hence the previous P V has finished: O_t is quiescent
+#pragma unroll
+                    for (int c = 0; c < D / 32; c++) {
+                        uint32_t o[32];
+                        tmem_ld_x32(o_addr + uint32_t(c) * 32u, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st_x32(o_addr + uint32_t(c) * 32u, o);
+                    }
+                    tmem_st_wait();
+                }
+                l *= f;
+                m = m_new;
+            }
+            const float m_ref = (m == -INFINITY) ? 0.f : m;
+            float bl4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk_lo[SPLIT ? 64 : 1];  // low parts wait in registers: their columns still hold unread scores
+            auto exp_chunk = [&](const uint32_t (&sv)[32], int c) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float x0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_ref));
+                    float x1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref));
+                    if (MASK) {
+                        if (c * 32 + 2 * i > visible) x0 = 0.f;
+                        if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
+                    }
+                    bl4[i & 3] += x0 + x1;
+                    pk[i] = pack2<IS_BF16>(x0, x1);
+                    if (SPLIT) {
+                        const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
+                        pk_lo[c * 16 + i] = pack2<true>(x0 - h0, x1 - h1);
+                    }
+                }
+                // keys 32c..32c+31 -> columns 16c..16c+15 of S_t (already consumed: they held keys < 32(c/2+1))
+                tmem_st_x16(s_addr + uint32_t(c) * 16u, pk);
+            };
+            // Pass 2, same two-deep pipeline (chunk 0 was requested at the end of pass 1; the rescale branch
+            // above waited for it if it ran, which is harmless).
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 32u, sb);
+            exp_chunk(sa, 0);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 64u, sa);
+            exp_chunk(sb, 1);
+            tmem_ld_wait();
+            tmem_ld_x32(s_addr + 96u, sb);
+            exp_chunk(sa, 2);
+            tmem_ld_wait();
+            exp_chunk(sb, 3);
+            if (SPLIT) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t part[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) part[i] = pk_lo[c * 16 + i];
+                    tmem_st_x16(s_addr + 64u + uint32_t(c) * 16u, part);
+                }
+            }
+            l += (bl4[0] + bl4[1]) + (bl4[2] + bl4[3]);
+            };
+            if (need_mask) block_body(std::true_type{});
+            else block_body(std::false_type{});
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(t));
+        }
+
+        if (ok) {
+            if (!mbar_wait(o_full(t), (o_cnt + uint32_t(n_t - 1)) & 1u)) {
+                if (lane == 0) attn_timeout(p.status, 36);
+                ok = false;
+            }
+            tc_fence_after();
+        }
+        o_cnt += uint32_t(n_t);
+        using T = typename std::conditional<SPLIT, float, typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type>::type;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        T* optr = static_cast<T*>(p.O) + b * p.os_b + h * p.os_h + (long long)row * p.os_s;
+        if (q0[t] < p.Sq) {
+#pragma unroll
+            for (int c = 0; c < D / 32; c++) {
+                uint32_t o[32];
+                if (n_t > 0 && ok) {
+                    tmem_ld_x32(o_addr + uint32_t(c) * 32u, o);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = 0u;
+                }
+                if (row < p.Sq && SPLIT) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 8; v4++) {
+                        float4 w;
+                        w.x = __uint_as_float(o[v4 * 4 + 0]) * inv;
+                        w.y = __uint_as_float(o[v4 * 4 + 1]) * inv;
+                        w.z = __uint_as_float(o[v4 * 4 + 2]) * inv;
+                        w.w = __uint_as_float(o[v4 * 4 + 3]) * inv;
+                        *reinterpret_cast<float4*>(reinterpret_cast<float*>(optr) + c * 32 + v4 * 4) = w;
+                    }
+                } else if (row < p.Sq) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++) {
+                        uint4 w;
+                        w.x = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 0]) * inv, __uint_as_float(o[v4 * 8 + 1]) * inv);
+                        w.y = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 2]) * inv, __uint_as_float(o[v4 * 8 + 3]) * inv);
+                        w.z = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 4]) * inv, __uint_as_float(o[v4 * 8 + 5]) * inv);
+                        w.w = pack2<IS_BF16>(__uint_as_float(o[v4 * 8 + 6]) * inv, __uint_as_float(o[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(optr) + c * 32 + v4 * 8) = w;
+                    }
+                }
+            }
+        }
+        // O_t is in registers / memory: the next item's first P V may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_empty(t));
+      }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 bool g_attr2_done[16][6] = {};
 
 template <int D, bool IS_BF16, bool SPLIT>
@@ -760,6 +1178,28 @@ int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, const AttnK
     const int64_t grid = p.B * p.H * ((kp.n_qtiles + 1) / 2);
     kern<<<unsigned(grid), 320, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
     return after_launch(ctx, "attention_tc2_kernel");
+}
+
+// Persistent variant (no causal mask): one CTA per SM walks the work items, so tensor-memory allocation, barrier set-up,
+// the first Q / K loads and the final store of O overlap the neighbouring items instead of costing every item its own
+// prologue and epilogue (with S = 512 an item is only four key blocks long).
+bool g_attr2p_done[16][6] = {};
+
+template <int D, bool IS_BF16, bool SPLIT>
+int launch2p(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, AttnKernelParams kp, int slot) {
+    constexpr int kTileBytes = (D / 64) * 16384;
+    constexpr int NS = attn2_slots(D, SPLIT);
+    constexpr size_t smem = size_t(kTileBytes) * (2 * (SPLIT ? 2 : 1) + NS) + 1024 + 256;
+    auto kern = attention_tc2p_kernel<D, IS_BF16, SPLIT>;
+    if (!g_attr2p_done[ctx->device & 15][slot]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        g_attr2p_done[ctx->device & 15][slot] = true;
+    }
+    const int64_t items = p.B * p.H * ((kp.n_qtiles + 1) / 2);
+    kp.n_items = int(items);
+    const int64_t grid = items < ctx->sm_count ? items : ctx->sm_count;
+    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
+    return after_launch(ctx, "attention_tc2p_kernel");
 }
 
 // fp32 [B,H,S,D] (strided, D contiguous) -> contiguous bf16 hi / lo planes.
@@ -840,6 +1280,12 @@ int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, c
     kp.status = ctx->status_dev;
     const bool bf = p.prec == DOCC_B200_PREC_B;
     static const bool single_tile = [] { const char* e = getenv("DOCC_B200_ATTENTION_SINGLE_TILE"); return e && e[0] == '1'; }();
+    static const bool persistent = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT"); return !e || e[0] != '0'; }();
+    if (!single_tile && p.Sq > kBQ && persistent && !p.causal) {
+        const CUtensorMap maps[6] = {tq, tk, tv, tq, tk, tv};
+        if (p.D == 128) return bf ? launch2p<128, true, false>(ctx, p, maps, kp, 0) : launch2p<128, false, false>(ctx, p, maps, kp, 1);
+        return bf ? launch2p<64, true, false>(ctx, p, maps, kp, 2) : launch2p<64, false, false>(ctx, p, maps, kp, 3);
+    }
     if (!single_tile && p.Sq > kBQ) {
         const CUtensorMap maps[6] = {tq, tk, tv, tq, tk, tv};
         if (p.D == 128) return bf ? launch2<128, true, false>(ctx, p, maps, kp, 0) : launch2<128, false, false>(ctx, p, maps, kp, 1);
@@ -895,6 +1341,8 @@ int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* 
     kp.scale_log2 = p.scale * 1.4426950408889634f;
     kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
     kp.status = ctx->status_dev;
+    static const bool persistent = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT"); return !e || e[0] != '0'; }();
+    if (persistent && !p.causal && p.Sq > kBQ) return launch2p<64, true, true>(ctx, p, maps, kp, 4);
     return launch2<64, true, true>(ctx, p, maps, kp, 4);
 }
 
