@@ -34,7 +34,7 @@ from docc_b200.sharding import gather_shards, shard  # noqa: E402
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from the ncu captures
 # summarised under profiles/ (softmax_rows_fp32_8192x4096.md, tc_gemm_pair_bf16_8192.md, conv_halo_bf16_config3.md,
 # attention_tc2_bf16_config4.md)
-NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5e6, "attention": 249.2e6}
+NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5e6, "attention": 244.6e6}
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
