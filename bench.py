@@ -332,6 +332,11 @@ def cpu_softmax_baseline(budget_s=12.0, max_reps=20):
     """Times the oracle (the reference's 7-loop-nest expansion, OpenMP on the outermost maps) on the full config."""
     import oracle
 
+    # all the host cores this process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
+    try:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        oracle.set_num_threads(os.cpu_count() or 1)
     rows, cols = 8192, 4096
     x = (3 * np.random.RandomState(1).randn(rows, cols)).astype(np.float32)
     oracle.softmax(x[:256], [1])

@@ -363,6 +363,15 @@ int oracle_num_threads() {
 #endif
 }
 
+// Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the timed baseline asks for the cores it may use.
+void oracle_set_num_threads(int n) {
+#if defined(_OPENMP)
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // alpha/beta as doubles; converted to the accumulate type inside.
 int oracle_gemm(int prec, int layout, int transa, int transb, int64_t m, int64_t n, int64_t k, double alpha,
                 const void* A, int64_t lda, const void* B, int64_t ldb, double beta, void* C, int64_t ldc) {

@@ -47,6 +47,11 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP team size for the following calls (launchers like torchrun export OMP_NUM_THREADS=1)."""
+    lib().oracle_set_num_threads(int(n))
+
+
 def _prec(dtype) -> int:
     dt = np.dtype(dtype)
     if dt == np.float64:
