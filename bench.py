@@ -8,8 +8,9 @@
 Prints ONE JSON line. The headline workload (default) is BASELINE config 2: row softmax over a
 fp32 [8192, 4096] tensor, reported as algorithmic HBM GB/s (one read + one write of the tensor).
 A "step" is one pass of the node over one batch of synthetic input. With --gpus N every rank
-processes its own batch (weak scaling, no data-path collective for softmax; the batch-sharded
-contraction workloads end with one NCCL all-gather of the output shards).
+processes its own batch (weak scaling over independent units, no data-path collective). ``--strong``
+instead splits ONE conv / attention / encoder-block configuration across the ranks and ends each step
+with one NCCL all-gather of the output shards.
 
 ``--impl reference`` times the CPU restatement of the reference's own expansion of the node
 (oracle/, OpenMP over the outermost map as docc's openmp target schedules it) on the host cores.
@@ -35,6 +36,11 @@ from docc_b200.sharding import gather_shards, shard  # noqa: E402
 # summarised under profiles/ (softmax_rows_fp32_8192x4096.md, tc_gemm_pair_bf16_8192.md, conv_halo_bf16_config3.md,
 # attention_tc2_bf16_config4.md)
 NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5e6, "attention": 244.6e6}
+
+# Sharded workloads (conv, attention, encoder block): by default every GPU runs the whole configuration on its own
+# data and nothing is exchanged (weak scaling over independent units). --strong splits ONE configuration across the
+# GPUs and ends each step with the NCCL all-gather of the output shards.
+STRONG = False
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -169,8 +175,10 @@ def make_workload(name, torch, ops, rank, world):
 
     if name in ("conv_f32", "conv_bf16"):
         n_total = 32
-        g.manual_seed(2)
-        x = shard(torch.randn(n_total, 64, 56, 56, generator=g), rank, world)
+        g.manual_seed(2 if STRONG else 2 + 1000 * rank)
+        x = torch.randn(n_total, 64, 56, 56, generator=g)
+        if STRONG:
+            x = shard(x, rank, world)
         n_local = x.shape[0]
         w = torch.nn.init.kaiming_normal_(torch.empty(128, 64, 3, 3), generator=g)
         bias = torch.zeros(128)
@@ -190,13 +198,17 @@ def make_workload(name, torch, ops, rank, world):
                     dtype="bf16" if name == "conv_bf16" else "f32(split-bf16x3)", bound="tensor",
                     peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None,
                     config={"workload": f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)",
-                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv", gather=n_total)
+                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv",
+                    gather=n_total if STRONG else None)
 
     if name in ("attention", "attention_causal"):
         causal = name.endswith("causal")
         bh_total = 8
-        g.manual_seed(3)
-        q, k, v = (shard(torch.randn(bh_total, 16, 2048, 128, generator=g), rank, world).bfloat16().to(dev) for _ in range(3))
+        g.manual_seed(3 if STRONG else 3 + 1000 * rank)
+        q, k, v = (torch.randn(bh_total, 16, 2048, 128, generator=g) for _ in range(3))
+        if STRONG:
+            q, k, v = (shard(t_, rank, world) for t_ in (q, k, v))
+        q, k, v = (t_.bfloat16().to(dev) for t_ in (q, k, v))
         b_local = q.shape[0]
 
         o = torch.empty_like(q)
@@ -213,19 +225,21 @@ def make_workload(name, torch, ops, rank, world):
                     bound="tensor", peak=peaks["bf16_tflops"], launches_per_step=1,
                     config={"workload": f"attention bf16 [8,16,2048,128] causal={causal} (BASELINE config 4)",
                             "batch_per_gpu": b_local, "l2": "flushed between steps"}, flush=True, kind="attention",
-                    gather=bh_total)
+                    gather=bh_total if STRONG else None)
 
     if name in ("block_f32", "block_bf16"):
         bf = name.endswith("bf16")
         b_total = 32
         d, heads, dff, seq = 1024, 16, 4096, 512
-        torch.manual_seed(4)
+        torch.manual_seed(4 if STRONG else 4 + 1000 * rank)
         p = {"ln1_g": torch.ones(d), "ln1_b": torch.zeros(d), "ln2_g": torch.ones(d), "ln2_b": torch.zeros(d)}
         for nm, shp in (("w_qkv", (3 * d, d)), ("w_o", (d, d)), ("w_1", (dff, d)), ("w_2", (d, dff))):
             p[nm] = torch.nn.init.xavier_uniform_(torch.empty(*shp))
         for nm, n in (("b_qkv", 3 * d), ("b_o", d), ("b_1", dff), ("b_2", d)):
             p[nm] = torch.zeros(n)
-        x = shard(torch.randn(b_total, seq, d), rank, world)
+        x = torch.randn(b_total, seq, d)
+        if STRONG:
+            x = shard(x, rank, world)
         b_local = x.shape[0]
         small = ("ln1_g", "ln1_b", "ln2_g", "ln2_b", "b_qkv", "b_o", "b_1", "b_2")
         pd = {k_: (v_.to(dev) if (k_ in small or not bf) else v_.bfloat16().to(dev)) for k_, v_ in p.items()}
@@ -241,7 +255,7 @@ def make_workload(name, torch, ops, rank, world):
                     peak=peaks["bf16_tflops_sustained"] / (1 if bf else 3), launches_per_step=None,
                     config={"workload": f"pre-LN encoder block {'bf16' if bf else 'fp32'} d1024 h16 ff4096 [32,512,1024] "
                                         "(BASELINE config 5)", "batch_per_gpu": b_local, "l2": "flushed between steps"},
-                    flush=True, kind="block", gather=b_total)
+                    flush=True, kind="block", gather=b_total if STRONG else None)
 
     raise SystemExit(f"unknown workload {name}")
 
@@ -376,6 +390,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="softmax")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--strong", action="store_true",
+                    help="split one conv / attention / block configuration across the GPUs and all-gather the outputs")
     ap.add_argument("--kernel-only", action="store_true", help="skip the e2e and CPU-baseline legs (profiling runs)")
     ap.add_argument("--extra-steps", type=int, default=10)
     args = ap.parse_args()
@@ -383,6 +399,8 @@ def main():
     if args.impl == "reference":
         run_reference(args)
         return
+    global STRONG
+    STRONG = bool(args.strong)
 
     import torch
     import torch.distributed as dist
@@ -412,7 +430,7 @@ def main():
 
     line = {"metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "replicas" if wl.get("replicas_only") else "weak", "vs_baseline": None, "dtype": wl["dtype"],
+            "scaling": "replicas" if wl.get("replicas_only") else ("strong" if (STRONG and wl.get("gather")) else "weak"), "vs_baseline": None, "dtype": wl["dtype"],
             "data": "synthetic", "config": wl["config"], "roofline": roof, "gpu_launches": int(launches), "clocks": clocks}
 
     if args.workload == "softmax" and not args.kernel_only:
