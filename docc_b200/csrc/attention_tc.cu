@@ -1,17 +1,16 @@
 // Flash attention on tcgen05: O = softmax(scale * Q K^T [+ causal mask]) V for 16-bit inputs,
 // head_dim 64 or 128, fp32 accumulation. The Sq x Skv score matrix never leaves the SM.
 //
-// One CTA owns a tile of 128 query rows of one (batch, head) and walks the key/value sequence
-// in blocks of 128. 192 threads:
-//   warp 0     TMA producer: Q once, then K_j / V_j into two-deep rings.
-//   warp 1     UMMA issuer:  S_j = Q K_j^T  (M=128, N=128, K=D) into one of two TMEM score buffers,
-//                            O_j = P_j V_j  (M=128, N=D,  K=128) into one of two TMEM output buffers.
-//   warps 2-5  softmax: thread r owns query row r. Per block: tcgen05.ld the row of S_j, running
-//              max / sum in the exp2 domain, P_j (16-bit) written to shared memory in the 128-byte
-//              swizzled K-major layout UMMA reads, then (one block later, so the tensor pipe never
-//              waits on it) acc = acc * corr_j + O_j from TMEM into registers.
-// QK^T of block j+1 is issued before P_j V_j, so the tensor pipe computes the next scores while the
-// softmax warps work on the current ones. All waits are bounded.
+// Three kernels, all with a TMA producer warp, a UMMA issuer warp and softmax warp groups in which thread r owns
+// query row r (running max / sum in the exp2 domain), and key/value blocks of 128:
+//   attention_tc_kernel    one 128-row query tile per CTA (sequences of at most 128 queries): S_j = Q K_j^T and
+//                          O_j = P_j V_j alternate between two TMEM buffers each, P_j goes through shared memory
+//                          in the 128-byte swizzled layout UMMA reads, O is accumulated in registers.
+//   attention_tc2_kernel   two query tiles per CTA, P and O resident in tensor memory (causal problems: one CTA
+//                          per pair of tiles, heaviest first).
+//   attention_tc2p_kernel  the same tile pair, persistent: one CTA per SM walks the (batch, head, pair) items of
+//                          an unmasked problem.
+// All waits are bounded.
 #include <cstdlib>
 #include <type_traits>
 

@@ -3,15 +3,17 @@
 // docc's expansion of ConvNode (conv_node.cpp:243-399) gives every output element its own
 // sequential C_in*kh*kw FMA chain. Here, per image,  Y_n[oc, pixel] = sum_{tap, c} W[oc, tap, c] *
 // X_n[pixel + tap, c]  is a GEMM with M = C_out, N = output pixels, K = kh*kw*C_in:
-//   1. one pass re-lays X from NCHW to NHWC 16-bit (fp32 input: bf16 hi and lo planes) and W from
+//   1. one launch re-lays X from NCHW to NHWC 16-bit (fp32 input: bf16 hi and lo planes) and W from
 //      [oc][c][kh][kw] to [oc][kh][kw][c], so that K is contiguous for both operands;
 //   2. a persistent warp-specialised kernel (same skeleton as the GEMM engine: TMA producer warp,
-//      UMMA issuer warp, four epilogue warps, two TMEM accumulators) walks tiles of 128 output
-//      channels x up to four output rows. For each filter tap the producer issues one TMA load per
-//      output row with the tap's (kh - pad, kw - pad) shift in the *outer* coordinates; rows and
-//      columns that fall outside the image are zero-filled by TMA, which is the zero padding.
-//   3. the accumulator tile is [oc lanes x pixel columns], i.e. already NCHW: every lane streams its
-//      channel's pixels straight to Y with the bias added.
+//      UMMA issuer warp, epilogue warps, two TMEM accumulators) walks tiles of 128 output channels
+//      x up to four output rows. Narrow images (conv_halo_kernel): the tile's input neighbourhood is
+//      loaded once per 64-channel block and every tap reads it through a shifted descriptor. Wide
+//      images (conv_tc_kernel): for each filter tap the producer issues one TMA load per output row
+//      with the tap's (kh - pad, kw - pad) shift in the *outer* coordinates. Rows and columns that
+//      fall outside the image are zero-filled by TMA, which is the zero padding;
+//   3. the accumulator tile is [oc lanes x pixel columns], i.e. already NCHW: it leaves through
+//      swizzled staging tiles and TMA stores with the bias added.
 // fp32 inputs run three passes (w_lo*x_hi, w_hi*x_lo, w_hi*x_hi) into the same accumulator.
 #include <cstdlib>
 #include <type_traits>

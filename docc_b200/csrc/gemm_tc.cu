@@ -4,20 +4,25 @@
 // Replaces the cublas{S,D}gemm call sequence of docc's CUDA target
 // (opt/src/targets/cuda/blas/gemm.cpp:131-185) for everything except fp64.
 //
-// Structure (one persistent CTA per SM, 320 threads):
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of 128x64 A tiles and BNx64 B tiles into a
-//               ring of 128-byte-swizzled shared-memory stages, completion on mbarriers.
-//   warp 1      UMMA issuer: one lane issues tcgen05.mma (M=128, N=BN, K=16) four times per stage;
+// Structure (one persistent CTA per SM, 320 threads; two kernels share it):
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A and B tiles (64 deep) into a ring of
+//               128-byte-swizzled shared-memory stages, completion on mbarriers.
+//   warp 1      UMMA issuer: one lane issues tcgen05.mma (K=16) four times per stage and tile half;
 //               tcgen05.commit releases the stage and, after the last k-block, publishes the
 //               accumulator. It also owns the tensor-memory allocation.
 //   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (each warp its own 32-lane quadrant),
-//               apply alpha/beta/bias/activation/residual, store.
-// Tiles are 256xBN (two M=128 UMMAs per k-step sharing the B tile; both 256-column TMEM regions
-// belong to one tile and each epilogue warp group drains one of them) or 128xBN (the two TMEM
-// regions are alternating accumulator buffers, so the epilogue of tile i overlaps the main loop
-// of tile i+1). fp32 operands are handled as split bf16 (hi + lo): the kernel runs up to three
-// passes (hi*hi, hi*lo, lo*hi) into the same accumulator, which keeps fp32-level accuracy
-// (~2^-16 relative per product) at a third of the bf16 rate. Every wait is bounded.
+//               apply alpha/beta/bias/activation/residual, stage and TMA-store.
+// tc_gemm_kernel (cta_group::1): tiles are 256xBN (two M=128 UMMAs per k-step sharing the B tile; both
+// 256-column TMEM regions belong to one tile and each epilogue warp group drains one of them) or
+// 128xBN (the two TMEM regions are alternating accumulator buffers, so the epilogue of tile i
+// overlaps the main loop of tile i+1); operands may be K-major or MN-major.
+// tc_gemm_pair_kernel (cta_group::2, K-major operands, large problems): a cluster of two CTAs owns a
+// 256x256 or 256x512 tile; each CTA loads its half of the rows of A and of B.
+// fp32 operands are handled as split bf16 (hi + lo): the kernels run up to three passes (hi*hi, hi*lo,
+// lo*hi) into the same accumulator, which keeps fp32-level accuracy (~2^-16 relative per product)
+// at a third of the bf16 rate. Every wait is bounded. Producer and issuer are single lanes: their
+// loops carry the ring position and the descriptors incrementally, because every scalar instruction
+// between two UMMAs is issue latency the tensor pipe has to absorb.
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
