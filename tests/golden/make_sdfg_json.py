@@ -109,6 +109,33 @@ def conv_relu():
     return b.finish()
 
 
+def matmul_add_mean_cast():
+    """Y = float64(mean(A @ B + C, axis=2)): batched MatMul with a broadcast right operand, Add, Mean, Cast."""
+    b = Builder("matmul_add_mean_cast")
+    for name in ("A", "B", "C"):
+        b.container(name, pointer(FLOAT), argument=True)
+    b.container("Y", pointer(DOUBLE), argument=True)
+    b.container("_s0", scalar(INT64), argument=True)
+    for name in ("t0", "t1", "t2"):
+        b.container(name, pointer(FLOAT))
+    a, bb, t0 = b.access("A"), b.access("B"), b.access("t0")
+    mm = b.library("ml::MatMul", shape_a=["_s0", "8", "16"], shape_b=["16", "12"], strides_a=["128", "16", "1"], strides_b=["12", "1"],
+                   offset_a="0", offset_b="0")
+    b.block([a, bb, t0, mm], [b.edge(a, "void", mm, "A", pointer(FLOAT)), b.edge(bb, "void", mm, "B", pointer(FLOAT)),
+                              b.edge(mm, "Y", t0, "void", pointer(FLOAT))])
+    t0_in, c, t1 = b.access("t0"), b.access("C"), b.access("t1")
+    add = b.library("ml::Add", shape=["_s0", "8", "12"])
+    b.block([t0_in, c, t1, add], [b.edge(t0_in, "void", add, "A", pointer(FLOAT)), b.edge(c, "void", add, "B", pointer(FLOAT)),
+                                  b.edge(add, "C", t1, "void", pointer(FLOAT))])
+    t1_in, t2 = b.access("t1"), b.access("t2")
+    mean = b.library("ml::Mean", shape=["_s0", "8", "12"], axes=[2], keepdims=False)
+    b.block([t1_in, t2, mean], [b.edge(t1_in, "void", mean, "X", pointer(FLOAT)), b.edge(mean, "Y", t2, "void", pointer(FLOAT))])
+    t2_in, y = b.access("t2"), b.access("Y")
+    cast = b.library("ml::Cast", shape=["_s0", "8"], target_type=DOUBLE)
+    b.block([t2_in, y, cast], [b.edge(t2_in, "void", cast, "X", pointer(FLOAT)), b.edge(cast, "Y", y, "void", pointer(DOUBLE))])
+    return b.finish()
+
+
 def with_tasklet():
     """A block with a scalar tasklet: outside what the reader executes."""
     b = Builder("scalar_code")
@@ -121,7 +148,8 @@ def with_tasklet():
 
 
 if __name__ == "__main__":
-    for name, fn in (("sdfg_gemm_softmax", gemm_softmax), ("sdfg_conv_relu", conv_relu), ("sdfg_scalar_code", with_tasklet)):
+    for name, fn in (("sdfg_gemm_softmax", gemm_softmax), ("sdfg_conv_relu", conv_relu), ("sdfg_matmul_add_mean_cast", matmul_add_mean_cast),
+                     ("sdfg_scalar_code", with_tasklet)):
         with open(os.path.join(HERE, name + ".json"), "w") as fh:
             json.dump(fn(), fh, indent=1, sort_keys=True)
             fh.write("\n")

@@ -109,3 +109,19 @@ def test_run_conv_relu(rt):
     y = np.zeros((nb, 6, 9, 10), np.float32)
     prog.run(x.ravel(), w.ravel(), bias, y.ravel(), nb)
     assert relerr(y, ref) <= 1e-4
+
+
+@pytest.mark.gpu
+def test_run_matmul_add_mean_cast(rt):
+    prog = sdfg_json.load(fixture("sdfg_matmul_add_mean_cast"))
+    assert prog.library_nodes() == ["ml::MatMul", "ml::Add", "ml::Mean", "ml::Cast"]
+    rng = np.random.RandomState(13)
+    nb = 5
+    a = rng.randn(nb, 8, 16).astype(np.float32)
+    b = rng.randn(16, 12).astype(np.float32)
+    c = rng.randn(nb, 8, 12).astype(np.float32)
+    summed = oracle.binary(0, oracle.matmul(a, b), c)  # binary op 0 = add
+    ref = oracle.reduce(oracle.RED_MEAN, summed, [2]).astype(np.float64)
+    y = np.zeros((nb, 8))
+    prog.run(a.ravel(), b.ravel(), c.ravel(), y.ravel(), nb)
+    assert y.dtype == np.float64 and relerr(y, ref) <= 1e-4
