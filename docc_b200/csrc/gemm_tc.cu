@@ -202,14 +202,21 @@ __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUt
             // the previous TMA store must have finished reading the staging tile
             if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
+            // 32 accumulator columns per tensor-memory load: half as many load/wait round trips per staging tile
 #pragma unroll
-            for (int sub = 0; sub < BOX / 16; sub++) {
-                uint32_t r[16];
-                tmem_ld_x16(t_addr + uint32_t(c0 + sub * 16), r);
+            for (int sub = 0; sub < BOX / 16; sub += 2) {
+                uint32_t r[32];
+                tmem_ld_x32(t_addr + uint32_t(c0 + sub * 16), r);
                 tmem_ld_wait();
-                float v[16];
-                epilogue_values<OutT, ACT>(p, r, row, n0 + c0 + sub * 16, b, row_ok, v);
-                epilogue_stage<OutT>(stage_base, lane, sub, v);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    uint32_t rh[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) rh[j] = r[h * 16 + j];
+                    float v[16];
+                    epilogue_values<OutT, ACT>(p, rh, row, n0 + c0 + (sub + h) * 16, b, row_ok, v);
+                    epilogue_stage<OutT>(stage_base, lane, sub + h, v);
+                }
             }
             fence_proxy_async_smem();
             __syncwarp();
