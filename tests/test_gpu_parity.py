@@ -459,7 +459,8 @@ def test_alloc_limit_reports_oom_without_touching_the_gpu(rt):
     try:
         p = _lib._vp()
         with pytest.raises(_lib.DoccB200Error) as e:
-            _lib.call("docc_b200_malloc", __import__("ctypes").byref(p), 3 << 20)  # a size no test used before
+            # a size class no other test allocates, so the pool cannot serve it from a cached block
+            _lib.call("docc_b200_malloc", __import__("ctypes").byref(p), (5 << 30) + (6 << 20))
         assert e.value.status == 4
     finally:
         _lib.call("docc_b200_set_alloc_limit", 0)
