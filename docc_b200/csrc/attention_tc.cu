@@ -771,8 +771,7 @@ __global__ void __launch_bounds__(320, 1)
     auto o_full = [&](int t) { return bars + 176u + 8u * uint32_t(t); };
     auto q_empty = [&](int t) { return bars + 192u + 8u * uint32_t(t); };  // issuer -> producer: Q_t may be overwritten
     auto o_empty = [&](int t) { return bars + 208u + 8u * uint32_t(t); };  // softmax group -> issuer: O_t has been stored
-    auto p_half = [&](int t) { return bars + 224u + 8u * uint32_t(t); };   // softmax group -> issuer: P of keys 0..63 is in place
-    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 240u - raw_addr));
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 224u - raw_addr));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = (p.n_qtiles + 1) / 2;
@@ -802,7 +801,6 @@ __global__ void __launch_bounds__(320, 1)
             mbar_init(o_full(t), 1);
             mbar_init(q_empty(t), 1);
             mbar_init(o_empty(t), 4);
-            mbar_init(p_half(t), 4);
         }
         fence_barrier_init();
         prefetch_tensormap(&tmQ);
@@ -925,33 +923,26 @@ __global__ void __launch_bounds__(320, 1)
                     if (j >= nb[t]) continue;
                     // the previous item's O_t must have left tensor memory before this item's first P V overwrites it
                     if (j == 0 && !mbar_wait(o_empty(t), (q_use[t] & 1u) ^ 1u)) { attn_timeout(p.status, 39); ok = false; break; }
-                    // 16-bit operands: the first half of P V (keys 0..63) starts while the softmax group still works on
-                    // the second half of the block
-                    if (!mbar_wait(SPLIT ? p_full(t) : p_half(t), p_cnt[t] & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
+                    if (!mbar_wait(p_full(t), p_cnt[t] & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
+                    p_cnt[t]++;
                     tc_fence_after();
                     const uint32_t o_tmem = tmem_base + 256u + uint32_t(t) * 128u;
                     const uint32_t p_hi = tmem_base + uint32_t(t) * 128u;  // P_t over the first 64 columns of S_t
                     const uint32_t p_lo = p_hi + 64u;                       // (fp32 path) low part over the last 64
                     uint32_t acc = j > 0 ? 1u : 0u;
-                    auto product = [&](uint32_t pa, uint32_t vb, int kk0, int kk1) {
+                    auto product = [&](uint32_t pa, uint32_t vb) {
                         const uint64_t vd = make_smem_desc(vb, 16384u, 1024u);
 #pragma unroll
-                        for (int kk = kk0; kk < kk1; kk++) {
+                        for (int kk = 0; kk < kBKV / 16; kk++) {
                             umma_f16_ts(o_tmem, pa + uint32_t(kk) * 8u, vd + uint64_t(kk * (2048 / 16)), idesc_pv, acc);
                             acc = 1;
                         }
                     };
                     if (SPLIT) {
-                        product(p_lo, v_hi, 0, kBKV / 16);
-                        product(p_hi, v_lo, 0, kBKV / 16);
-                        product(p_hi, v_hi, 0, kBKV / 16);
-                    } else {
-                        product(p_hi, v_hi, 0, kBKV / 32);
-                        if (!mbar_wait(p_full(t), p_cnt[t] & 1u)) { attn_timeout(p.status, 34); ok = false; break; }
-                        tc_fence_after();
-                        product(p_hi, v_hi, kBKV / 32, kBKV / 16);
+                        product(p_lo, v_hi);
+                        product(p_hi, v_lo);
                     }
-                    p_cnt[t]++;
+                    product(p_hi, v_hi);
                     umma_commit(o_full(t));
                     if (j + 1 < nb[t]) {
                         issue_qk(t, k_hi, k_lo);
@@ -1087,12 +1078,6 @@ __global__ void __launch_bounds__(320, 1)
             tmem_ld_wait();
             tmem_ld_x32(s_addr + 64u, sa);
             exp_chunk(sb, 1);
-            if (!SPLIT) {  // P of keys 0..63 is complete: let the first half of P V go
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_half(t));
-            }
             tmem_ld_wait();
             tmem_ld_x32(s_addr + 96u, sb);
             exp_chunk(sa, 2);
