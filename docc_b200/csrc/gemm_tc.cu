@@ -882,7 +882,7 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         else {
             bm = 256;
             bn = 256;
-            const bool wide_ok = pair_mode == 2 || (pair_mode == 1 && K * npass >= 4096);
+            const bool wide_ok = pair_mode == 2 || (pair_mode == 1 && K * npass >= 4096);  // pair_mode 3: never
             if (wide_ok && t512 >= pairs && double(ceil_div(t512, pairs)) * 512 <= double(ceil_div(t256, pairs)) * 256 * 1.05) bn = 512;
         }
     }
