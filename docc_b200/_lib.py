@@ -47,6 +47,7 @@ SIGNATURES = {
     "docc_b200_strerror": (ctypes.c_char_p, [_int]),
     "docc_b200_last_error": (ctypes.c_char_p, []),
     "docc_b200_launch_count": (_i64, [_int]),
+    "docc_b200_selftest_wait_timeout": (_int, [_i64]),
     "docc_b200_gemm": (_int, [_int, _int, _int, _int, _i64, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _int]),
     "docc_b200_gemm_f32_noalloc": (_int, [_int, _int, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i64, _f32, _vp, _i64, _vp]),
     "docc_b200_matmul": (_int, [_int, _i64, _i64, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _int]),

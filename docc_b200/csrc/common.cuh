@@ -56,6 +56,7 @@ struct Ctx {
     cudaStream_t stream = nullptr;      // the stream launches go to (own_stream unless overridden)
     cudaStream_t copy_streams[2] = {nullptr, nullptr};
     cudaEvent_t copy_events[4] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t switch_event = nullptr;  // orders a newly selected stream after the one it replaces
     void* workspace[4] = {nullptr, nullptr, nullptr, nullptr};  // library-owned scratch, grows on demand
     size_t workspace_bytes[4] = {0, 0, 0, 0};
     DeviceStatus* status_host = nullptr;  // mapped pinned

@@ -23,7 +23,8 @@ struct GemmView {
 
 struct SimtEpilogue {
     double alpha, beta;
-    const float* bias;     // per column
+    const void* bias;      // per column; fp64 when bias_f64 (the 'd' path), fp32 otherwise
+    bool bias_f64;
     int act;
     const void* residual;  // same type as C
     int64_t ldr;
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A,
             if (col >= g.N) continue;
             Acc v = Acc(ep.alpha) * acc[i][j];
             if (ep.beta != 0.0) v += Acc(ep.beta) * to_acc(C[row * g.ldc + col], Acc(0));
-            if (ep.bias) v += Acc(ep.bias[col]);
+            if (ep.bias) v += ep.bias_f64 ? Acc(static_cast<const double*>(ep.bias)[col]) : Acc(static_cast<const float*>(ep.bias)[col]);
             if (ep.act != DOCC_B200_ACT_NONE) {
                 if constexpr (sizeof(Acc) == 8) v = apply_act_f64(ep.act, v);
                 else v = apply_act(ep.act, v);
@@ -286,7 +287,7 @@ struct GemmCall {
     GemmView g;
     int64_t batch;
     double alpha, beta;
-    const float* bias;
+    const void* bias;  // element type of C for 's' and 'd', fp32 for 16-bit operands
     int act;
     const void* residual;
     int64_t ldr;
@@ -297,7 +298,7 @@ struct GemmCall {
 int gemm_device(Ctx* ctx, const GemmCall& c, const void* A, const void* B, void* C) {
     const GemmView& g = c.g;
     if (g.M == 0 || g.N == 0 || c.batch == 0) return DOCC_B200_OK;
-    SimtEpilogue sep{c.alpha, c.beta, c.bias, c.act, c.residual, c.ldr};
+    SimtEpilogue sep{c.alpha, c.beta, c.bias, c.prec == DOCC_B200_PREC_D, c.act, c.residual, c.ldr};
     if (c.prec == DOCC_B200_PREC_D) {
         if (c.bias || c.act != DOCC_B200_ACT_NONE || c.residual) return launch_simt<double>(ctx, A, B, C, g, sep, c.batch);
         return launch_dmma(ctx, A, B, C, g, c.alpha, c.beta, c.batch);
@@ -306,7 +307,7 @@ int gemm_device(Ctx* ctx, const GemmCall& c, const void* A, const void* B, void*
     if (want_tc) {
         TcEpilogue ep;
         ep.alpha = float(c.alpha); ep.beta = float(c.beta);
-        ep.bias = c.bias; ep.bias_mode = c.bias ? 1 : 0; ep.act = c.act;
+        ep.bias = static_cast<const float*>(c.bias); ep.bias_mode = c.bias ? 1 : 0; ep.act = c.act;
         ep.residual = c.residual; ep.ldr = c.ldr; ep.residual_batch_stride = g.c_bs;
         ep.out = C; ep.ldo = g.ldc; ep.out_batch_stride = g.c_bs; ep.out_prec = c.prec;
         int s = run_tc(ctx, c.prec, A, B, g, c.batch, ep);
@@ -341,9 +342,10 @@ int gemm_host(Ctx* ctx, const GemmCall& c, const void* A, const void* B, void* C
     if (c.beta != 0.0 || g.ldc != g.N) DOCC_CUDA_TRY(cudaMemcpyAsync(dC, C, c_n * es, cudaMemcpyHostToDevice, ctx->stream));
     GemmCall d = c;
     if (c.bias) {
-        DOCC_TRY(tmp.alloc(&dBias, size_t(g.N) * 4));
-        DOCC_CUDA_TRY(cudaMemcpyAsync(dBias, c.bias, size_t(g.N) * 4, cudaMemcpyHostToDevice, ctx->stream));
-        d.bias = static_cast<const float*>(dBias);
+        const size_t bias_bytes = size_t(g.N) * (c.prec == DOCC_B200_PREC_D ? 8 : 4);
+        DOCC_TRY(tmp.alloc(&dBias, bias_bytes));
+        DOCC_CUDA_TRY(cudaMemcpyAsync(dBias, c.bias, bias_bytes, cudaMemcpyHostToDevice, ctx->stream));
+        d.bias = dBias;
     }
     if (c.residual) {
         const size_t r_n = (c.batch - 1) * size_t(g.c_bs) + span_elems(g.M, g.N, c.ldr, 1);
@@ -462,7 +464,7 @@ extern "C" int docc_b200_gemm_epilogue(int prec, int transb, int64_t m, int64_t 
     c.g.b_rs = tb ? 1 : ldb; c.g.b_cs = tb ? ldb : 1;
     c.g.ldc = ldy; c.g.a_bs = c.g.b_bs = c.g.c_bs = 0;
     c.batch = 1; c.alpha = alpha; c.beta = 0.0;
-    c.bias = static_cast<const float*>(bias); c.act = act; c.residual = residual; c.ldr = ldr; c.flags = flags;
+    c.bias = bias; c.act = act; c.residual = residual; c.ldr = ldr; c.flags = flags;
     if (flags & DOCC_B200_FLAG_HOST_PTRS) return gemm_host(ctx, c, A, B, Y);
     return gemm_device(ctx, c, A, B, Y);
 }

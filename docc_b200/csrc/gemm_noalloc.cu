@@ -79,9 +79,15 @@ extern "C" int docc_b200_gemm_f32_noalloc(int transa, int transb, int64_t m, int
     DOCC_REQUIRE(A && B && C, "gemm_f32_noalloc: NULL matrix pointer");
     const bool ta = transa == DOCC_B200_TRANS, tb = transb == DOCC_B200_TRANS;
     DOCC_REQUIRE(lda >= (ta ? m : k) && ldb >= (tb ? k : n) && ldc >= n, "gemm_f32_noalloc: leading dimension too small");
+    // extents of a problem that fits are far below 2^31; checking first keeps the size product from wrapping
+    DOCC_REQUIRE(m <= INT32_MAX && n <= INT32_MAX && k <= INT32_MAX - 8, "gemm_f32_noalloc: extent exceeds 2^31 - 1");
     const int64_t kp = round_up8(k);
-    const size_t need = size_t(4) * size_t(m + n) * size_t(kp);  // hi + lo planes of A and of B, 2 bytes each
-    if (need > kNoAllocScratchBytes) {
+    // hi + lo planes of A and of B, 2 bytes each. The comparison divides so that no product can wrap; `need` is only
+    // formed for the message when it is known to be huge, where saturating is good enough.
+    const bool too_big = uint64_t(m + n) > kNoAllocScratchBytes / 4 / uint64_t(kp);
+    const size_t need = too_big && uint64_t(m + n) > (UINT64_MAX / 4) / uint64_t(kp) ? SIZE_MAX
+                                                                                     : size_t(4) * size_t(m + n) * size_t(kp);
+    if (too_big) {
         return set_error(DOCC_B200_ERR_INVALID_ARG,
                          "gemm_f32_noalloc: problem needs %zu bytes of scratch (4*(m+n)*roundup8(k)) but the built-in array holds "
                          "%zu; use docc_b200_gemm for larger products",

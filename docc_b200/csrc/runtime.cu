@@ -16,10 +16,20 @@ namespace {
 thread_local char tls_error[512] = "";
 thread_local Ctx tls_ctx[16];
 
+// The pool is stream ordered: a freed block remembers the stream it was freed on and an event recorded there at the
+// moment of the free. The next owner gets it at once when it allocates on the same stream (work queued there runs
+// after the previous owner's), and otherwise its stream is made to wait for the event (cudaStreamWaitEvent), so a
+// kernel of the previous owner that is still running can never overlap the new owner's work. Nothing blocks the host.
+struct FreeBlock {
+    void* ptr;
+    cudaStream_t stream;  // stream the block was freed on
+    cudaEvent_t event;    // recorded on that stream at the free; nullptr when the freeing thread had synchronised
+};
 struct Pool {
     std::mutex mu;
-    std::multimap<size_t, void*> free_blocks;      // rounded size -> block
+    std::multimap<size_t, FreeBlock> free_blocks;  // rounded size -> block
     std::unordered_map<void*, size_t> live;        // handed-out block -> rounded size
+    std::vector<cudaEvent_t> spare_events;         // events of reused blocks, recycled
     size_t held = 0;                               // bytes obtained from the driver
 };
 Pool g_pools[16];
@@ -66,6 +76,7 @@ int get_ctx(Ctx** out) {
         DOCC_CUDA_TRY(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
         for (auto& s : c->copy_streams) DOCC_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
         for (auto& ev : c->copy_events) DOCC_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        DOCC_CUDA_TRY(cudaEventCreateWithFlags(&c->switch_event, cudaEventDisableTiming));
         void* h = nullptr;
         DOCC_CUDA_TRY(cudaHostAlloc(&h, sizeof(DeviceStatus), cudaHostAllocMapped));
         memset(h, 0, sizeof(DeviceStatus));
@@ -80,18 +91,53 @@ int get_ctx(Ctx** out) {
     return DOCC_B200_OK;
 }
 
+namespace {
+// The stream the calling thread's launches go to on device `dev` (nullptr before the thread's first call there).
+cudaStream_t current_stream_of_thread(int dev) {
+    const Ctx& c = tls_ctx[dev & 15];
+    return c.device == dev ? c.stream : nullptr;
+}
+}  // namespace
+
 int pool_alloc(void** dptr, size_t bytes) {
     int dev = 0;
     DOCC_CUDA_TRY(cudaGetDevice(&dev));
     Pool& p = g_pools[dev & 15];
     const size_t r = round_size(bytes);
+    const cudaStream_t stream = current_stream_of_thread(dev);
     {
-        std::lock_guard<std::mutex> lock(p.mu);
-        auto it = p.free_blocks.find(r);
-        if (it != p.free_blocks.end()) {
-            *dptr = it->second;
-            p.live[it->second] = r;
-            p.free_blocks.erase(it);
+        std::unique_lock<std::mutex> lock(p.mu);
+        auto range = p.free_blocks.equal_range(r);
+        auto pick = range.second;
+        for (auto it = range.first; it != range.second; ++it) {  // same stream first: no wait at all
+            if (it->second.event == nullptr || it->second.stream == stream) {
+                pick = it;
+                break;
+            }
+            if (pick == range.second) pick = it;
+        }
+        if (pick != range.second) {
+            FreeBlock b = pick->second;
+            p.free_blocks.erase(pick);
+            p.live[b.ptr] = r;
+            lock.unlock();
+            if (b.event) {
+                cudaError_t e = cudaSuccess;
+                if (b.stream != stream) {
+                    // the block's last use was queued on another stream: order this thread's stream after it
+                    e = stream ? cudaStreamWaitEvent(stream, b.event, 0) : cudaEventSynchronize(b.event);
+                }
+                std::lock_guard<std::mutex> relock(p.mu);
+                p.spare_events.push_back(b.event);
+                if (e != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    p.free_blocks.emplace(r, FreeBlock{b.ptr, nullptr, nullptr});
+                    p.live.erase(b.ptr);
+                    return set_error(DOCC_B200_ERR_CUDA, "ordering a reused block after its previous owner failed: %s",
+                                     cudaGetErrorString(e));
+                }
+            }
+            *dptr = b.ptr;
             return DOCC_B200_OK;
         }
         if (g_alloc_limit && p.held + r > g_alloc_limit) {
@@ -108,7 +154,8 @@ int pool_alloc(void** dptr, size_t bytes) {
         {
             std::lock_guard<std::mutex> lock(p.mu);
             for (auto& kv : p.free_blocks) {
-                to_free.push_back(kv.second);
+                to_free.push_back(kv.second.ptr);
+                if (kv.second.event) p.spare_events.push_back(kv.second.event);
                 p.held -= kv.first;
             }
             p.free_blocks.clear();
@@ -134,11 +181,37 @@ int pool_free(void* dptr) {
     int dev = 0;
     DOCC_CUDA_TRY(cudaGetDevice(&dev));
     Pool& p = g_pools[dev & 15];
+    const cudaStream_t stream = current_stream_of_thread(dev);
+    cudaEvent_t ev = nullptr;
+    size_t r = 0;
+    {
+        std::lock_guard<std::mutex> lock(p.mu);
+        auto it = p.live.find(dptr);
+        if (it == p.live.end()) return set_error(DOCC_B200_ERR_INVALID_ARG, "pointer %p was not allocated by docc_b200_malloc", dptr);
+        r = it->second;
+        p.live.erase(it);
+        if (!p.spare_events.empty()) {
+            ev = p.spare_events.back();
+            p.spare_events.pop_back();
+        }
+    }
+    // Mark the point on the freeing thread's stream after which the block is no longer in use. If that cannot be done
+    // (no stream yet, or the event calls fail) the free falls back to waiting for the device, which is always safe.
+    bool marked = false;
+    if (stream) {
+        if (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) ev = nullptr;
+        if (ev && cudaEventRecord(ev, stream) == cudaSuccess) marked = true;
+    }
+    if (!marked) {
+        (void)cudaGetLastError();
+        (void)cudaDeviceSynchronize();
+    }
     std::lock_guard<std::mutex> lock(p.mu);
-    auto it = p.live.find(dptr);
-    if (it == p.live.end()) return set_error(DOCC_B200_ERR_INVALID_ARG, "pointer %p was not allocated by docc_b200_malloc", dptr);
-    p.free_blocks.emplace(it->second, dptr);
-    p.live.erase(it);
+    if (!marked && ev) {
+        p.spare_events.push_back(ev);
+        ev = nullptr;
+    }
+    p.free_blocks.emplace(r, FreeBlock{dptr, stream, ev});
     return DOCC_B200_OK;
 }
 
@@ -208,11 +281,13 @@ int docc_b200_shutdown(void) {
     {
         std::lock_guard<std::mutex> lock(p.mu);
         for (auto& kv : p.free_blocks) {
-            to_free.push_back(kv.second);
+            to_free.push_back(kv.second.ptr);
+            if (kv.second.event) p.spare_events.push_back(kv.second.event);
             p.held -= kv.first;
         }
         p.free_blocks.clear();
     }
+    (void)cudaDeviceSynchronize();  // blocks freed on other threads' streams may still be in use there
     for (void* q : to_free) (void)cudaFree(q);
     return DOCC_B200_OK;
 }
@@ -228,8 +303,7 @@ int docc_b200_free(void* dptr) {
     if (!dptr) return DOCC_B200_OK;
     Ctx* c;
     DOCC_TRY(get_ctx(&c));
-    // a block may be reused by another stream right away: finish this thread's work on it first
-    DOCC_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    // asynchronous: the pool orders the block's next owner after the work queued on this thread's stream so far
     return pool_free(dptr);
 }
 
@@ -275,7 +349,20 @@ int docc_b200_set_alloc_limit(size_t bytes) {
 int docc_b200_set_stream(void* stream) {
     Ctx* c;
     DOCC_TRY(get_ctx(&c));
-    c->stream = stream ? static_cast<cudaStream_t>(stream) : c->own_stream;
+    const cudaStream_t next = stream ? static_cast<cudaStream_t>(stream) : c->own_stream;
+    if (next != c->stream) {
+        // The thread's workspaces (operand planes, block intermediates) and the buffers it handed out are ordered on
+        // one stream at a time. Work already queued on the old stream may still use them, so the new stream is made
+        // to wait for it; the host does not block.
+        cudaEvent_t ev = c->switch_event;
+        cudaError_t e = cudaEventRecord(ev, c->stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(next, ev, 0);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            DOCC_CUDA_TRY(cudaDeviceSynchronize());  // e.g. the old stream handle was destroyed by its owner
+        }
+        c->stream = next;
+    }
     return DOCC_B200_OK;
 }
 

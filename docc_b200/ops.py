@@ -4,6 +4,13 @@ Each function accepts either numpy arrays (host memory: the call stages the data
 through the device, docc's "WithTransfers" flavour) or torch CUDA tensors (device
 pointers, asynchronous on the library's current stream). Mixed inputs are an error.
 Outputs have the kind of the inputs.
+
+Stream ordering of device calls: the library's current stream is, by default, a private
+non-blocking stream of the calling thread that is NOT ordered after torch's streams. Code that
+mixes torch operations and these calls on the same tensors must either route the library to
+torch's stream first (``set_stream(torch.cuda.current_stream().cuda_stream)``, which the front
+ends in ``docc_b200.torch`` / ``docc_b200.python`` do on every call) or synchronise around the
+calls (``torch.cuda.synchronize()`` before, ``sync()`` after).
 """
 from __future__ import annotations
 
@@ -238,6 +245,13 @@ def linear(X, W, bias=None, act=ACT_NONE, residual=None, alpha=1.0, flags=0):
     k = X.shape[-1]
     m = int(np.prod(X.shape[:-1]))
     n = W.shape[0]
+    # the ABI sees pointers and leading dimensions only: extents and types are checked here
+    if W.ndim != 2 or W.shape[1] != k or _prec(W) != _prec(X):
+        raise ValueError(f"linear: weight {tuple(W.shape)} does not match inputs of width {k} and type {chr(_prec(X))!r}")
+    if bias is not None and int(np.prod(bias.shape)) != n:
+        raise ValueError(f"linear: bias has {int(np.prod(bias.shape))} elements for {n} output features")
+    if residual is not None and (tuple(residual.shape) != tuple(X.shape[:-1]) + (n,) or _prec(residual) != _prec(X)):
+        raise ValueError("linear: the residual must have the shape and type of the output (broadcast it first)")
     Y = _empty(X, tuple(X.shape[:-1]) + (n,))
     call("docc_b200_gemm_epilogue", _prec(X), TRANS, m, n, k, float(alpha), _ptr(X), k, _ptr(W), k, _ptr(bias), int(act),
          _ptr(residual), n, _ptr(Y), n, flags)

@@ -40,21 +40,51 @@ def register_target_overrides(name, schedule_fn, compile_fn):
 
 
 def install_docc_overrides() -> bool:
-    """When docc itself is importable, registers a ``"b200"`` target with it that links generated code
-    against ``libdocc_b200_rt.so``. Returns False when docc is not installed."""
+    """When docc itself is importable, registers a ``"b200"`` target with it through docc's own hook
+    (``register_target_overrides``, python/docc/python/target_registry.py:22-43). Returns False when docc is
+    not installed.
+
+    * ``schedule_fn(sdfg, category, options)`` forwards to ``sdfg.schedule("b200", category, remote_tuning)``: in a
+      docc built with the B200 plugin that branch runs ``b200_scheduling_passes`` (the library-node mapper), the way
+      the ``etsoc`` branch runs ``et_scheduling_passes`` (python/bindings/py_structured_sdfg.cpp:302-348).
+    * ``compile_fn(sdfg, output_folder, instrumentation_mode, capture_args, options)`` calls the binding exactly as
+      it is declared, ``_compile(output_folder, target, instrumentation_mode, capture_args)``
+      (python/bindings/bindings.cpp:166-172). That signature has no room for extra flags, and the stock driver only
+      adds target flags for the names it knows (py_structured_sdfg.cpp:486-550), so the header and the runtime reach
+      the compiler through its environment (``CPATH`` for ``#include <docc_b200/rt.h>``, ``LIBRARY_PATH`` for the
+      linker), and ``libdocc_b200_rt.so`` is loaded into the process with global visibility first so that the
+      generated library's ``docc_b200_*`` references resolve when ``CompiledSDFG`` opens it with ``ctypes.CDLL``.
+      A docc rebuilt with the plugin passes the same flags itself (``b200_get_host_additional_compile_args`` /
+      ``b200_get_host_additional_link_args``); the environment route is then redundant and harmless.
+    """
     try:
         from docc.python import target_registry  # type: ignore
     except Exception:
         return False
-    from ..build import INCLUDE, LIB_DIR
+    import ctypes
+    import os
 
-    def schedule_fn(sdfg, category, options):
-        return None  # node mapping happens in the C++ plugin's TargetMappingPass
+    from ..build import INCLUDE, LIB_DIR, LIB_PATH
 
-    def compile_fn(sdfg, out_dir, instrumentation_mode, capture_args, options):
-        return sdfg._compile(out_dir, "b200", instrumentation_mode, capture_args,
-                             extra_compile_args=f"-I{INCLUDE}",
-                             extra_link_args=f"-L{LIB_DIR} -Wl,-rpath,{LIB_DIR} -ldocc_b200_rt")
+    def schedule_fn(sdfg, category, options=None):
+        sdfg.schedule("b200", category, bool((options or {}).get("remote_tuning", False)))
+
+    def _prepend(var, value):
+        old = os.environ.get(var)
+        os.environ[var] = value if not old else value + os.pathsep + old
+        return old
+
+    def compile_fn(sdfg, output_folder, instrumentation_mode, capture_args, options=None):
+        ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        saved = {var: _prepend(var, val) for var, val in (("CPATH", INCLUDE), ("LIBRARY_PATH", LIB_DIR))}
+        try:
+            return sdfg._compile(output_folder, "b200", instrumentation_mode, capture_args)
+        finally:
+            for var, old in saved.items():
+                if old is None:
+                    os.environ.pop(var, None)
+                else:
+                    os.environ[var] = old
 
     target_registry.register_target_overrides("b200", schedule_fn, compile_fn)
     return True

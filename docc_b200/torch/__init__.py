@@ -76,8 +76,17 @@ _ACT = {"gelu": ops.ACT_GELU_ERF, "relu": ops.ACT_RELU, "tanh": ops.ACT_TANH, "s
 
 # ---- lowering of single operations -----------------------------------------------------------------
 def _linear(x, w, bias=None, act=ops.ACT_NONE, residual=None):
+    if residual is not None:
+        # The epilogue reads the residual as a full [.., out_features] tensor of the output type. An addend that
+        # broadcasts (a bias-like vector, a [1, S, d] table) or has another type goes through the add node instead.
+        out_shape = tuple(x.shape[:-1]) + (w.shape[0],)
+        if not isinstance(residual, torch.Tensor) or tuple(residual.shape) != out_shape or residual.dtype != x.dtype:
+            return _binary("add")(_linear(x, w, bias, act), residual)
     node = N.LinearNode(act=act, has_bias=bias is not None, has_residual=residual is not None)
-    return _dispatch(node, _contig(x), _contig(w), _f32(bias), _contig(residual) if residual is not None else None)
+    if bias is not None:  # the epilogue reads the bias in the output type for fp32 / fp64 and as fp32 for 16-bit layers
+        bias = _contig(bias) if x.dtype == torch.float64 and bias.dtype == torch.float64 else (
+            ops.cast(_contig(bias), torch.float64) if x.dtype == torch.float64 else _f32(bias))
+    return _dispatch(node, _contig(x), _contig(w), bias, _contig(residual) if residual is not None else None)
 
 
 def _matmul(a, b):
@@ -92,7 +101,9 @@ def _matmul(a, b):
     return _dispatch(N.MatMulNode(), _contig(a), _contig(b))
 
 
-def _softmax(x, dim=-1):
+def _softmax(x, dim=-1, _stacklevel=3, dtype=None):
+    if dtype is not None and dtype != x.dtype:
+        raise UnsupportedGraph("softmax with a dtype= conversion")
     return _dispatch(N.SoftmaxNode(axes=[dim]), _contig(x))
 
 
@@ -113,6 +124,9 @@ def _sdpa(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, e
         raise UnsupportedGraph("attention masks, dropout and grouped-query attention")
     B, H, Sq, D = q.shape
     Skv = k.shape[2]
+    if is_causal and Sq != Skv:
+        # torch aligns the causal mask with the first key, the kernels with the last one; the two agree only for Sq == Skv
+        raise UnsupportedGraph("is_causal with different query and key lengths")
     if scale is None:
         scale = 1.0 / math.sqrt(D)
     # Output is laid out [B, S, H, D] so that the transpose(1, 2).reshape(B, S, H*D) that follows in a
@@ -154,6 +168,10 @@ def _binary(kind):
     def fn(a, b, *args, **kwargs):
         if kwargs.get("alpha", 1) != 1:
             raise UnsupportedGraph("alpha on add/sub")
+        if kwargs.get("rounding_mode") is not None:
+            raise UnsupportedGraph("div with a rounding mode")
+        if kwargs.get("out") is not None:
+            raise UnsupportedGraph("out= arguments")
         ta, tb = isinstance(a, torch.Tensor), isinstance(b, torch.Tensor)
         if ta and tb:
             if a.shape == b.shape and a.dtype == b.dtype:
@@ -183,16 +201,16 @@ def _binary(kind):
 _FUNCTIONS: Dict[object, Callable] = {
     F.linear: _linear, torch._C._nn.linear: _linear,
     torch.matmul: _matmul, operator.matmul: _matmul, torch.mm: _matmul, torch.bmm: _matmul,
-    F.softmax: lambda x, dim=-1, **kw: _softmax(x, dim), torch.softmax: lambda x, dim=-1, **kw: _softmax(x, dim),
+    F.softmax: _softmax, torch.softmax: _softmax,
     F.conv2d: _conv2d, torch.conv2d: _conv2d,
     F.scaled_dot_product_attention: _sdpa, torch._C._nn.scaled_dot_product_attention: _sdpa,
     F.layer_norm: _layer_norm,
     F.gelu: _unary("gelu"), torch._C._nn.gelu: _unary("gelu"), F.relu: _unary("relu"), torch.relu: _unary("relu"),
     torch.tanh: _unary("tanh"), F.tanh: _unary("tanh"), torch.sigmoid: _unary("sigmoid"), F.sigmoid: _unary("sigmoid"),
     torch.exp: _unary("exp"), torch.erf: _unary("erf"), torch.sqrt: _unary("sqrt"), torch.abs: _unary("abs"),
-    operator.add: _binary("add"), operator.iadd: _binary("add"), torch.add: _binary("add"),
+    operator.add: _binary("add"), torch.add: _binary("add"),
     operator.sub: _binary("sub"), torch.sub: _binary("sub"),
-    operator.mul: _binary("mul"), operator.imul: _binary("mul"), torch.mul: _binary("mul"),
+    operator.mul: _binary("mul"), torch.mul: _binary("mul"),
     operator.truediv: _binary("div"), torch.div: _binary("div"),
     operator.getitem: lambda x, idx: x[idx],
     torch.transpose: lambda x, a, b: x.transpose(a, b), torch.permute: lambda x, dims: x.permute(dims),
@@ -201,12 +219,15 @@ _FUNCTIONS: Dict[object, Callable] = {
     torch.unbind: lambda x, *a, **k: x.unbind(*a, **k),
 }
 
+_INPLACE_FUNCTIONS = {operator.iadd: "add", operator.imul: "mul", operator.isub: "sub", operator.itruediv: "div"}
+_INPLACE_METHODS = {"add_": "add", "mul_": "mul", "sub_": "sub", "div_": "div"}
+
 # tensor methods that only change metadata (views); .contiguous() materialises through a copy
 _VIEW_METHODS = {"view", "reshape", "transpose", "permute", "flatten", "unsqueeze", "squeeze", "t", "size", "chunk", "split",
                  "unbind", "contiguous", "expand", "unflatten", "dim"}
 _METHODS: Dict[str, Callable] = {
-    "softmax": lambda x, dim=-1, **kw: _softmax(x, dim), "matmul": _matmul, "mm": _matmul, "bmm": _matmul,
-    "add": _binary("add"), "add_": _binary("add"), "mul": _binary("mul"), "sub": _binary("sub"), "div": _binary("div"),
+    "softmax": _softmax, "matmul": _matmul, "mm": _matmul, "bmm": _matmul,
+    "add": _binary("add"), "mul": _binary("mul"), "sub": _binary("sub"), "div": _binary("div"),
     "relu": _unary("relu"), "tanh": _unary("tanh"), "sigmoid": _unary("sigmoid"), "exp": _unary("exp"),
 }
 
@@ -235,6 +256,8 @@ class _Lowered:
                 self.steps.append(("attr", n.name, n.target))
             elif n.op == "call_function":
                 fn = _FUNCTIONS.get(n.target)
+                if fn is None and n.target in _INPLACE_FUNCTIONS:
+                    fn = self._inplace(n, _INPLACE_FUNCTIONS[n.target])
                 if fn is None and getattr(n.target, "__module__", "") in ("_operator", "operator", "builtins", "math"):
                     # shape arithmetic on Python / symbolic integers (dynamic shapes): host scalars, not tensor work
                     self.steps.append(("scalar", n.name, n.target, n.args, dict(n.kwargs)))
@@ -261,7 +284,9 @@ class _Lowered:
                 self.steps.append(("call", out_name, fn, args, kwargs))
                 self.n_library_nodes += 1
             elif n.op == "call_method":
-                if n.target in _METHODS:
+                if n.target in _INPLACE_METHODS:
+                    self.steps.append(("call", n.name, self._inplace(n, _INPLACE_METHODS[n.target]), n.args, dict(n.kwargs)))
+                elif n.target in _METHODS:
                     self.steps.append(("call", n.name, _METHODS[n.target], n.args, dict(n.kwargs)))
                 elif n.target in _VIEW_METHODS:
                     self.steps.append(("method", n.name, n.target, n.args, dict(n.kwargs)))
@@ -273,6 +298,16 @@ class _Lowered:
                 raise UnsupportedGraph("un-inlined module call; compile with dynamo's default inlining")
             elif n.op == "output":
                 self.output = n.args[0]
+
+    @staticmethod
+    def _inplace(n: torch.fx.Node, kind: str):
+        """``x += y`` / ``x.add_(y)`` on a value this graph produced: the node's result stands for the updated tensor
+        in every later use, so computing it out of place is equivalent. On a graph input or parameter the caller would
+        have to see the update, which this path does not do."""
+        dst = n.args[0] if n.args else None
+        if not isinstance(dst, torch.fx.Node) or dst.op in ("placeholder", "get_attr"):
+            raise UnsupportedGraph(f"in-place {kind} on a graph input or parameter")
+        return _binary(kind)
 
     @staticmethod
     def _defined_before(a: torch.fx.Node, b: torch.fx.Node) -> bool:

@@ -97,8 +97,11 @@ int docc_b200_device_count(void);
 
 /* Device allocation / free: 1:1 with the ALLOC / FREE lifecycle of
  * CUDADataOffloadingNode (cuda_data_offloading_node.cpp:149-158,166-172).
- * Backed by a size-bucketed pool so repeated alloc/free pairs around a node
- * cost no cudaMalloc. */
+ * Backed by a size-bucketed, stream-ordered pool so repeated alloc/free pairs
+ * around a node cost no cudaMalloc and no host synchronisation: free marks the
+ * calling thread's stream, and whoever gets the block next (any thread, any
+ * stream) is ordered after that mark on the device. Use a buffer only on the
+ * stream that was current when it was allocated, or order the streams yourself. */
 int docc_b200_malloc(void** dptr, size_t bytes);
 int docc_b200_free(void* dptr);
 /* H2D / D2H copies: the two transfer directions of CUDADataOffloadingNode
@@ -116,7 +119,11 @@ int docc_b200_set_alloc_limit(size_t bytes);
 /* Stream control. `stream` is a cudaStream_t; NULL restores the library's own
  * per-thread stream. CUDA's special handles cudaStreamLegacy ((cudaStream_t)0x1)
  * and cudaStreamPerThread ((cudaStream_t)0x2) name the default streams.
- * Replaces the implicit default stream of generated code. */
+ * Replaces the implicit default stream of generated code.
+ * The calling thread's library-owned workspaces (operand planes, block
+ * intermediates) are ordered on one stream at a time: switching makes the new
+ * stream wait, on the device, for the work queued on the old one. The old
+ * stream must still exist when the switch is made. */
 int docc_b200_set_stream(void* stream);
 int docc_b200_get_stream(void** stream);
 /* Waits for everything queued on the calling thread's stream
@@ -127,6 +134,12 @@ const char* docc_b200_strerror(int status);
 const char* docc_b200_last_error(void);
 /* Number of kernels this library launched from the calling thread since the last reset. */
 int64_t docc_b200_launch_count(int reset);
+/* Self-test of the bounded-wait error path (no reference counterpart; docc's generated
+ * kernels have no waits). Launches one warp that waits, for at most `limit_cycles` SM
+ * clocks, on a shared-memory barrier nothing arrives at; the warp then gives up exactly
+ * as the tensor-core kernels do: it sets the status word and returns. The following
+ * docc_b200_sync() returns DOCC_B200_ERR_DEVICE_TIMEOUT once and clears the word. */
+int docc_b200_selftest_wait_timeout(int64_t limit_cycles);
 
 /* ---- GEMM -------------------------------------------------------------------
  * C[m x n] = alpha * op(A) * op(B) + beta * C, the GEMMNode contract
@@ -172,8 +185,10 @@ int docc_b200_matmul(int prec, int64_t batch, int64_t m, int64_t n, int64_t k,
  * elementwise_node.cpp:86-339 that follow it in a transformer block):
  *   Y = act(alpha * A*op(B) + bias[n]) + residual
  * Row-major. transb == DOCC_B200_TRANS reads B as [n x k] (torch Linear weight).
- * prec 's': fp32 in/out; 'b': bf16 in/out (bias fp32, residual bf16).
- * bias / residual may be NULL. ldr is the residual's row stride. */
+ * prec 's': fp32 in/out; 'd': fp64 in/out; 'b' / 'h': 16-bit in/out. The bias has the
+ * element type of Y for 's' and 'd' and is fp32 for 16-bit operands; the residual has
+ * the type of Y and at least m rows of n elements (row stride ldr >= n).
+ * bias / residual may be NULL. */
 int docc_b200_gemm_epilogue(int prec, int transb, int64_t m, int64_t n, int64_t k,
                             float alpha, const void* A, int64_t lda,
                             const void* B, int64_t ldb,

@@ -91,6 +91,54 @@ def test_registry_first_registration_wins():
         reg.dispatch(nodes.GEMMNode(inputs=["a", "b"], outputs=["c"], implementation_type="Y"), {})
 
 
+def test_install_docc_overrides_calls_the_bindings_as_they_are_declared(monkeypatch, tmp_path):
+    """A stand-in ``docc.python.target_registry`` records what gets registered; a stand-in SDFG records how the hooks
+    call it. ``_compile`` is bound as (output_folder, target, instrumentation_mode, capture_args) and ``schedule`` as
+    (target, category, remote_tuning) (python/bindings/bindings.cpp:157-172); the hooks themselves are invoked with
+    the argument lists of python/docc/python/python_program.py:289-314."""
+    import sys
+    import types
+
+    import docc_b200.python as dpy
+    from docc_b200 import build
+
+    registered = {}
+    docc, pkg, reg = types.ModuleType("docc"), types.ModuleType("docc.python"), types.ModuleType("docc.python.target_registry")
+    reg.register_target_overrides = lambda name, schedule_fn, compile_fn=None: registered.update({name: (schedule_fn, compile_fn)})
+    docc.python, pkg.target_registry = pkg, reg
+    for name, mod in (("docc", docc), ("docc.python", pkg), ("docc.python.target_registry", reg)):
+        monkeypatch.setitem(sys.modules, name, mod)
+    assert dpy.install_docc_overrides() is True
+    schedule_fn, compile_fn = registered["b200"]
+
+    class FakeSDFG:
+        def __init__(self):
+            self.calls = []
+
+        def schedule(self, target, category, remote_tuning=False):  # exactly the bound parameters
+            self.calls.append(("schedule", target, category, remote_tuning))
+
+        def _compile(self, output_folder, target, instrumentation_mode="", capture_args=False):
+            import os
+
+            self.calls.append(("_compile", output_folder, target, instrumentation_mode, capture_args))
+            self.env = (os.environ.get("CPATH", ""), os.environ.get("LIBRARY_PATH", ""))
+            return output_folder + "/libx.so"
+
+    sdfg = FakeSDFG()
+    schedule_fn(sdfg, "server", {"remote_tuning": False})
+    monkeypatch.setenv("CPATH", "/somewhere/else")
+    monkeypatch.delenv("LIBRARY_PATH", raising=False)
+    assert compile_fn(sdfg, str(tmp_path), "ols", True, {}) == str(tmp_path) + "/libx.so"
+    assert sdfg.calls == [("schedule", "b200", "server", False), ("_compile", str(tmp_path), "b200", "ols", True)]
+    # the header and the library were on the compiler's search paths during the call, and only during the call
+    import os
+
+    assert sdfg.env[0].split(os.pathsep)[0] == build.INCLUDE and "/somewhere/else" in sdfg.env[0]
+    assert sdfg.env[1] == build.LIB_DIR
+    assert os.environ["CPATH"] == "/somewhere/else" and "LIBRARY_PATH" not in os.environ
+
+
 class Block(nn.Module):
     def __init__(self, d=64, heads=4, dff=128):
         super().__init__()
@@ -129,6 +177,57 @@ def test_transformer_block_lowers_with_fused_epilogues():
     assert sum(1 for k in fused if k.get("act")) == 1  # fc1 -> GELU
     assert sum(1 for k in fused if k.get("residual") is not None) == 2  # proj + x, fc2 + x
     assert "gelu" not in " ".join(fns) and not any(s[2].__name__ == "fn" and False for s in calls)
+
+
+def test_linear_plus_broadcast_addend_is_not_folded_into_the_epilogue(monkeypatch):
+    # The epilogue's residual is a full [.., out] tensor of the output type. `linear(x) + pos` with a broadcasting or
+    # differently typed addend must run as linear followed by the add node, never hand the short buffer to the kernel.
+    seen = []
+    monkeypatch.setattr(docc_torch, "_dispatch", lambda node, *inputs: seen.append((node, inputs)) or torch.zeros(2, 8, 16))
+    added = []
+    monkeypatch.setattr(docc_torch, "_binary", lambda kind: (lambda a, b: added.append((kind, tuple(b.shape), b.dtype)) or a))
+    x, w = torch.randn(2, 8, 4), torch.randn(16, 4)
+    for other in (torch.randn(16), torch.randn(1, 8, 16), torch.randn(2, 8, 16, dtype=torch.float64)):
+        seen.clear(), added.clear()
+        docc_torch._linear(x, w, None, residual=other)
+        assert len(seen) == 1 and not seen[0][0].has_residual and seen[0][1][3] is None
+        assert added == [("add", tuple(other.shape), other.dtype)]
+    seen.clear(), added.clear()
+    docc_torch._linear(x, w, None, residual=torch.randn(2, 8, 16))  # exact shape and type: fused
+    assert seen[0][0].has_residual and not added
+
+
+def test_frontend_refuses_semantics_it_would_get_wrong():
+    class CausalCross(nn.Module):
+        def forward(self, q, k):
+            return F.scaled_dot_product_attention(q, k, k, is_causal=True)
+
+    low = lower_on_cpu(CausalCross(), torch.randn(1, 1, 4, 8), torch.randn(1, 1, 6, 8))
+    sdpa = next(s for s in low.steps if s[0] == "call")
+    with pytest.raises(docc_torch.UnsupportedGraph):
+        sdpa[2](torch.randn(1, 1, 4, 8), torch.randn(1, 1, 6, 8), torch.randn(1, 1, 6, 8), is_causal=True)
+    with pytest.raises(docc_torch.UnsupportedGraph):
+        docc_torch._softmax(torch.randn(2, 2), -1, dtype=torch.float64)
+    with pytest.raises(docc_torch.UnsupportedGraph):
+        docc_torch._binary("div")(torch.randn(2), torch.randn(2), rounding_mode="floor")
+
+    class InPlaceOnInput(nn.Module):
+        def forward(self, x, y):
+            x += y
+            return x
+
+    with pytest.raises(Exception) as e:
+        lower_on_cpu(InPlaceOnInput(), torch.randn(3), torch.randn(3))
+    assert "in-place" in str(e.value)
+
+    class InPlaceOnIntermediate(nn.Module):
+        def forward(self, x, y):
+            z = x * y
+            z += y
+            return z
+
+    low = lower_on_cpu(InPlaceOnIntermediate(), torch.randn(3), torch.randn(3))
+    assert sum(1 for s in low.steps if s[0] == "call") == 2
 
 
 def test_unsupported_torch_op_raises_instead_of_falling_back():
@@ -244,6 +343,33 @@ def test_torch_backend_transformer_block(rt, docc_cuda):
     ref = mb(xb)
     out = torch.compile(mb, backend="docc")(xb)
     assert out.is_cuda and relerr(out.detach().float().cpu().numpy(), ref.detach().float().cpu().numpy()) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_torch_backend_linear_plus_position_table_and_fp64_bias(rt, docc_cuda):
+    class WithPos(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = nn.Linear(32, 48)
+            self.pos = nn.Parameter(torch.randn(1, 6, 48))
+            self.vec = nn.Parameter(torch.randn(48))
+
+        def forward(self, x):
+            return (self.lin(x) + self.pos) if x.dim() == 3 else (self.lin(x) + self.vec)
+
+    torch.manual_seed(9)
+    m = WithPos().eval()
+    x2 = torch.randn(5, 32)
+    assert torch.allclose(torch.compile(m, backend="docc")(x2), m(x2), rtol=1e-4, atol=1e-5)
+    x3 = torch.randn(4, 6, 32)
+    torch._dynamo.reset()
+    with pytest.raises(Exception) as e:  # [1, S, d] broadcast: refused by the add node, never read out of bounds
+        torch.compile(m, backend="docc")(x3)
+    assert "broadcasting" in str(e.value)
+    torch._dynamo.reset()
+    m64 = nn.Linear(24, 40).double().eval()
+    x64 = torch.randn(7, 24, dtype=torch.float64)
+    assert torch.allclose(torch.compile(m64, backend="docc")(x64), m64(x64), rtol=1e-12, atol=1e-12)
 
 
 @pytest.mark.gpu

@@ -189,6 +189,21 @@ def test_linear_fused_epilogue(rt):
     assert relerr(ops.linear(x, w, bias, ops.ACT_GELU_ERF, res), ref) <= TOL_F32  # host pointers
 
 
+def test_linear_fp64_bias_is_read_as_fp64(rt):
+    rng = np.random.RandomState(14)
+    x, w = rng.randn(50, 40), rng.randn(30, 40)
+    bias, res = rng.randn(30), rng.randn(50, 30)
+    ref = x @ w.T + bias + res
+    assert relerr(host(ops.linear(dev(x), dev(w), dev(bias), residual=dev(res))), ref) <= TOL_F64
+    assert relerr(ops.linear(x, w, bias, residual=res), ref) <= TOL_F64  # host pointers: staged as 8-byte elements
+    with pytest.raises(TypeError):
+        ops.linear(x, w, bias.astype(np.float32))
+    with pytest.raises(ValueError):
+        ops.linear(x, w, bias, residual=res[:1])  # a residual that would have to broadcast
+    with pytest.raises(ValueError):
+        ops.linear(x, w[:, :39], bias)
+
+
 # ---- softmax / reductions ----------------------------------------------------------------------------
 def test_softmax_config2(rt):
     torch.manual_seed(1)
@@ -338,6 +353,41 @@ def test_attention_bf16(rt, B, H, S, D, causal):
     assert relerr(got, ref) <= TOL_16
 
 
+# fp32 attention with head_dim 64 runs on the tensor cores as bf16 hi/lo planes (three products per contraction).
+# Longer than one 128-row tile it takes the two-tile kernels: persistent without a mask (B*H*ceil(S/256) above the
+# SM count makes every CTA walk several items), one CTA per tile pair with a causal mask. These are the kernels the
+# fp32 encoder block of BASELINE config 5 (16 heads of 64, sequence 512) launches.
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,S", [(1, 2, 256), (2, 3, 384), (6, 16, 512), (1, 2, 300), (1, 1, 129)])
+def test_attention_fp32_head64_multi_tile(rt, B, H, S, causal):
+    rng = np.random.RandomState(S + B)
+    q, k, v = (rng.randn(B, H, S, 64).astype(np.float32) for _ in range(3))
+    ref = oracle.attention(q, k, v, causal=causal)
+    got = host(ops.attention(dev(q), dev(k), dev(v), causal=causal))
+    assert relerr(got, ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_fp32_cross_lengths(rt, causal):
+    # Sq != Skv: the causal mask aligns the last query with the last key
+    rng = np.random.RandomState(17)
+    q = rng.randn(2, 2, 256, 64).astype(np.float32)
+    k, v = (rng.randn(2, 2, 448, 64).astype(np.float32) for _ in range(2))
+    ref = oracle.attention(q, k, v, causal=causal)
+    assert relerr(host(ops.attention(dev(q), dev(k), dev(v), causal=causal)), ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,S,D", [(5, 16, 512, 64), (3, 20, 640, 128)])
+def test_attention_bf16_persistent_walk(rt, B, H, S, D, causal):
+    # more (batch, head, tile pair) items than SMs: the persistent kernel's hand-over between items
+    torch.manual_seed(S)
+    q, k, v = (torch.randn(B, H, S, D).bfloat16() for _ in range(3))
+    ref = oracle.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), causal=causal)
+    got = host(ops.attention(q.cuda(), k.cuda(), v.cuda(), causal=causal))
+    assert relerr(got, ref) <= TOL_16
+
+
 def test_attention_config4_properties(rt):
     # full config 4; the oracle checks two (batch, head) slices, the rest through properties
     torch.manual_seed(3)
@@ -435,6 +485,66 @@ def test_transformer_block_bf16(rt):
     assert relerr(got, ref) <= TOL_16
 
 
+# BASELINE config 5 at its own geometry (d_model 1024, 16 heads of 64, FFN 4096, sequence 512) with a reduced batch:
+# same tiles, same attention instantiation (two-tile persistent, head_dim 64; hi/lo planes for fp32) and same fused
+# epilogues as the benchmarked block. The oracle composes the block from the restated nodes; torch in fp64 is the
+# second opinion on the whole output.
+def torch_block_f64(x, p, heads):
+    import torch.nn.functional as F
+
+    x = x.double().cuda()  # cuBLAS fp64 on the device: a second opinion, not the oracle
+    p = {k: v.double().cuda() for k, v in p.items()}
+    Bn, S, d = x.shape
+    h1 = F.layer_norm(x, (d,), p["ln1_g"], p["ln1_b"])
+    qkv = F.linear(h1, p["w_qkv"], p["b_qkv"]).reshape(Bn, S, 3, heads, d // heads)
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(Bn, S, d)
+    h = x + F.linear(a, p["w_o"], p["b_o"])
+    f = F.gelu(F.linear(F.layer_norm(h, (d,), p["ln2_g"], p["ln2_b"]), p["w_1"], p["b_1"]))
+    return (h + F.linear(f, p["w_2"], p["b_2"])).cpu().numpy()
+
+
+def make_block_nontrivial(d, dff, seed=4):
+    # config 5 has zero biases and unit LayerNorm scales; random ones make the bias and LayerNorm paths visible
+    p = make_block(d, dff, seed)
+    g = torch.Generator().manual_seed(seed + 100)
+    for name in ("b_qkv", "b_o", "b_1", "b_2", "ln1_b", "ln2_b"):
+        p[name] = torch.randn(p[name].shape, generator=g) * 0.1
+    for name in ("ln1_g", "ln2_g"):
+        p[name] = torch.rand(p[name].shape, generator=g) + 0.5
+    return p
+
+
+@pytest.mark.parametrize("batch,maker", [(1, make_block), (2, make_block_nontrivial), (10, make_block_nontrivial)])
+def test_transformer_block_config5_geometry_fp32(rt, batch, maker):
+    d, heads, dff, seq = 1024, 16, 4096, 512
+    p = maker(d, dff)
+    torch.manual_seed(40 + batch)
+    x = torch.randn(batch, seq, d)
+    got = host(ops.transformer_block(x.cuda(), {k: v.cuda() for k, v in p.items()}, heads))
+    assert relerr(got, torch_block_f64(x, p, heads)) <= TOL_F32
+    nb = min(batch, 2)  # sequences are independent: the oracle takes the first two
+    ref = oracle.transformer_block(x[:nb].numpy(), {k: v.numpy() for k, v in p.items()}, heads)
+    assert relerr(got[:nb], ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("batch,maker", [(1, make_block), (2, make_block_nontrivial), (10, make_block_nontrivial)])
+def test_transformer_block_config5_geometry_bf16(rt, batch, maker):
+    d, heads, dff, seq = 1024, 16, 4096, 512
+    p = maker(d, dff)
+    torch.manual_seed(50 + batch)
+    small = ("ln1_g", "ln1_b", "ln2_g", "ln2_b", "b_qkv", "b_o", "b_1", "b_2")
+    p16 = {k: (v if k in small else v.bfloat16()) for k, v in p.items()}
+    x = torch.randn(batch, seq, d).bfloat16()
+    got = host(ops.transformer_block(x.cuda(), {k: v.cuda() for k, v in p16.items()}, heads))
+    # the fp32 reference sees the same rounded weights and input
+    pf = {k: v.float() for k, v in p16.items()}
+    assert relerr(got, torch_block_f64(x.float(), pf, heads)) <= TOL_16
+    nb = min(batch, 2)
+    ref = oracle.transformer_block(x[:nb].float().numpy(), {k: v.numpy() for k, v in pf.items()}, heads)
+    assert relerr(got[:nb], ref) <= TOL_16
+
+
 # ---- runtime behaviour ---------------------------------------------------------------------------------------------
 def test_pool_and_transfers(rt):
     p = _lib._vp()
@@ -464,6 +574,83 @@ def test_alloc_limit_reports_oom_without_touching_the_gpu(rt):
         assert e.value.status == 4
     finally:
         _lib.call("docc_b200_set_alloc_limit", 0)
+
+
+def test_pool_is_stream_ordered_across_threads(rt):
+    # This thread queues a long chain of kernels that keep rewriting a pooled block with 1.0 and frees the block
+    # without waiting. Another host thread (its own non-blocking stream) then gets the same block and fills it
+    # with 2.0. The pool has to order the second stream after the queued chain on the device: if the fill could
+    # overtake the chain, the chain's late writes would put 1.0 back.
+    import ctypes
+    import threading
+
+    n = 64 << 20  # one 64 MiB block: a size class no other test leaves in the pool
+    rows, cols = n // 4 // 4096, 4096
+    ones = np.full(n // 4, 1.0, dtype=np.float32)
+    twos = torch.full((n // 4,), 2.0).pin_memory()
+    p = _lib._vp()
+    _lib.call("docc_b200_malloc", ctypes.byref(p), n)
+    _lib.call("docc_b200_h2d", p, ones.ctypes.data, n)
+    for _ in range(400):  # ~25 us each: about 10 ms of queued work that writes the block
+        _lib.call("docc_b200_bias_act", ord("s"), rows, cols, p, 1.0, None, 0, None, p, 0)
+    _lib.call("docc_b200_free", p)  # returns at once
+    got = {}
+
+    def other_thread():
+        torch.cuda.set_device(0)
+        ops.init(0)
+        q = _lib._vp()
+        _lib.call("docc_b200_malloc", ctypes.byref(q), n)
+        got["ptr"] = q.value
+        _lib.call("docc_b200_h2d", q, twos.data_ptr(), n)
+        torch.cuda.synchronize()  # the first thread's chain has finished too
+        out = np.empty(n // 4, dtype=np.float32)
+        _lib.call("docc_b200_d2h", out.ctypes.data, q, n)
+        got["data"] = out
+        _lib.call("docc_b200_free", q)
+
+    t = threading.Thread(target=other_thread)
+    t.start()
+    t.join()
+    ops.sync()
+    assert got["ptr"] == p.value  # the pool did hand over the block that had just been freed
+    assert np.all(got["data"] == 2.0)
+
+
+def test_set_stream_orders_the_new_stream_after_the_old(rt):
+    # an fp32 GEMM keeps bf16 planes of its operands in a per-thread workspace; a second GEMM routed to another
+    # stream right away must not rewrite the planes while the first one still reads them
+    torch.manual_seed(31)
+    a1, b1 = torch.randn(2048, 2048, device="cuda"), torch.randn(2048, 2048, device="cuda")
+    a2, b2 = torch.randn(2048, 2048, device="cuda"), torch.randn(2048, 2048, device="cuda")
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    try:
+        for _ in range(3):
+            ops.set_stream(s1.cuda_stream)
+            c1 = ops.gemm(a1, b1)
+            ops.set_stream(s2.cuda_stream)
+            c2 = ops.gemm(a2, b2)
+            torch.cuda.synchronize()
+            assert ((c1.double() - a1.double() @ b1.double()).abs().max() / 2048 ** 0.5).item() <= 1e-3
+            assert ((c2.double() - a2.double() @ b2.double()).abs().max() / 2048 ** 0.5).item() <= 1e-3
+    finally:
+        ops.set_stream(torch.cuda.current_stream().cuda_stream)
+
+
+def test_bounded_device_wait_reports_a_timeout_and_the_context_survives(rt):
+    # one warp waits ~1e5 clocks (about 50 us) on a barrier nothing arrives at, gives up, and sets the status word
+    _lib.call("docc_b200_selftest_wait_timeout", 100000)
+    with pytest.raises(_lib.DoccB200Error) as e:
+        ops.sync()
+    assert e.value.status == 6 and "location code 900" in str(e.value)
+    ops.sync()  # reported once, then cleared
+    x = torch.randn(64, 256, device="cuda")
+    y = ops.softmax(x, [-1])  # the context is still usable
+    ops.sync()
+    assert relerr(host(y), torch.softmax(x, -1).cpu().numpy()) <= TOL_F32
+    with pytest.raises(_lib.DoccB200Error):
+        _lib.call("docc_b200_selftest_wait_timeout", 0)
 
 
 def test_invalid_arguments_are_rejected(rt):
