@@ -42,6 +42,7 @@ struct ConvKernelParams {
     int tiles_m;
     long long total_units;  // tiles_m * N * Ho output-row units
     int w_stages;  // halo variant: depth of the weight ring
+    int x_chunks;  // fused variant: depth of the input staging ring
     int tma_out;  // Y rows are 16-byte aligned: full 32-pixel groups go out through TMA stores
     const float* bias;
     float* Y;
@@ -580,6 +581,430 @@ __device__ __forceinline__ void weight_relayout(const TIn* __restrict__ Wt, __nv
     }
 }
 
+// ---- fused variant: 16-bit NCHW input read in place ----------------------------------------------------
+// Same tiling, tap addressing, weight ring and epilogue as conv_halo_kernel, but the input never takes a trip through an
+// NHWC copy in HBM. NCHW keeps the pixels of one channel contiguous, whereas the tensor cores want, per pixel slot,
+// the 64 channels of a block contiguous (K-major rows of 128 bytes, 128-byte swizzle). A one-pixel tap shift is 2
+// bytes in NCHW, below the 16-byte granularity of TMA coordinates and shared-memory descriptors alike, so neither
+// can do the transposition. It happens between two shared-memory buffers instead:
+//   * a producer warp brings one input row of a 64-channel block at a time, [64 channels][64 pixels] (8 KB, 128-byte
+//     swizzle), through a ring of staging chunks by TMA. The box starts 8 pixels left of the image when there is left
+//     padding (x coordinate -8: 16 bytes, the TMA alignment rule); rows above / below the image and columns outside
+//     it are zero-filled by TMA, which is the convolution's zero padding;
+//   * four transposer warps move each chunk into the tile's halo slot with ldmatrix.trans / stmatrix: four 8x8 blocks
+//     [8 channels][8 pixels] come out as [8 pixels][8 channels], and every 16-byte row is stored at the swizzled
+//     position of its pixel slot (slot = staging pixel - 8 + pad_w). Both sides are bank-conflict free because both
+//     layouts are 128-byte swizzled. Slots the box does not reach (the right padding) are written as zeros.
+// Plain per-thread global loads were measured first (8 warps x 24-48 loads of 4 bytes in flight): the SM's load path
+// could not keep enough of them outstanding, a tile's input took 8k clocks against 6k for its tensor-core work.
+// The halo slots are double buffered: tile i+1 is assembled while the tensor core works on tile i.
+// The weights come from the small re-laid copy ([oc][tap][c], written by conv_weights_kernel just before); this
+// kernel is launched with programmatic stream serialization and only its weight producer waits for that copy
+// (griddepcontrol.wait), so set-up, tensor-memory allocation and the first input rows overlap it.
+// Requirements (checked by the host): 16-bit input, W % 8 == 0, X 16-byte aligned, Wo + kw - 1 <= 64,
+// pad_w <= 8 and W <= 56, or pad_w == 0 and W <= 64.
+// Warps: 0 weight producer, 1 UMMA issuer, 2-9 epilogue, 10-13 transposers, 14 input producer.
+constexpr int kFusedThreads = 480;
+constexpr uint32_t kChunkBytes = 64 * 64 * 2;  // one input row of a channel block
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, const uint32_t (&r)[4]) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+                 : "memory");
+}
+
+template <bool IS_BF16>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+    conv_nchw_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmX,
+                     const __grid_constant__ CUtensorMap tmY, const ConvKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    const uint32_t halo_rows_max = uint32_t(p.r_max + p.kh - 1);
+    const uint32_t halo_bytes = halo_rows_max * 8192u;
+    const uint32_t w_stages = uint32_t(p.w_stages);
+    const uint32_t n_chunks = uint32_t(p.x_chunks);
+    const uint32_t sH = base;                           // halo slots; reads past a slot's end land in the next region
+    const uint32_t sA = sH + kHaloSlots * halo_bytes;   // weight ring
+    const uint32_t sX = sA + w_stages * kABytes;        // staging chunks of the input producer
+    const uint32_t sStage = sX + n_chunks * kChunkBytes;  // eight 4 KB staging tiles (one per epilogue warp)
+    const uint32_t sDummy = sStage + 8 * 4096u;         // 512 bytes: target of stmatrix rows that belong to no slot
+    const uint32_t bars = sDummy + 512u;
+    auto full_a = [&](uint32_t i) { return bars + 8u * i; };
+    auto empty_a = [&](uint32_t i) { return bars + 64u + 8u * i; };
+    auto full_h = [&](uint32_t i) { return bars + 128u + 8u * i; };
+    auto empty_h = [&](uint32_t i) { return bars + 144u + 8u * i; };
+    auto tfull_bar = [&](uint32_t i) { return bars + 160u + 8u * i; };
+    auto tempty_bar = [&](uint32_t i) { return bars + 176u + 8u * i; };
+    auto full_x = [&](uint32_t i) { return bars + 192u + 8u * i; };
+    auto empty_x = [&](uint32_t i) { return bars + 256u + 8u * i; };
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 320u - raw_addr));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp == 0 && lane == 0) {
+        for (uint32_t i = 0; i < w_stages; i++) {
+            mbar_init(full_a(i), 1);
+            mbar_init(empty_a(i), 1);
+        }
+        for (uint32_t i = 0; i < 2; i++) {
+            mbar_init(full_h(i), 4);  // one arrival per transposer warp
+            mbar_init(empty_h(i), 1);
+            mbar_init(tfull_bar(i), 1);
+            mbar_init(tempty_bar(i), 8);
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmW0);
+        prefetch_tensormap(&tmY);
+    }
+    const long long u_begin = p.total_units * blockIdx.x / gridDim.x;
+    const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
+    const int cblocks = p.C / 64;
+    const int x0 = p.pad_w > 0 ? -8 : 0;  // first input column of a staging chunk
+    // The input producer owns the barriers of its ring and fills the ring before the block-wide synchronisation: the
+    // first rows (a trip to HBM) are then in flight while tensor memory is allocated and the other barriers are set up.
+    uint32_t x_early = 0;
+    if (warp == 14 && lane == 0) {
+        for (uint32_t i = 0; i < n_chunks; i++) {
+            mbar_init(full_x(i), 1);
+            mbar_init(empty_x(i), 4);  // one arrival per transposer warp
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmX);
+        long long u = u_begin;
+        Tile t;
+        if (next_tile(p, u, u_end, t)) {
+            const uint32_t hrows = uint32_t(t.rows + p.kh - 1);
+            x_early = hrows < n_chunks ? hrows : n_chunks;
+            for (uint32_t i = 0; i < x_early; i++) {
+                mbar_arrive_expect_tx(full_x(i), kChunkBytes);
+                tma_load_4d(sX + i * kChunkBytes, &tmX, full_x(i), x0, t.oh0 - p.pad_h + int(i), 0, t.n);
+            }
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
+        if (lane == 0) {
+            griddep_wait();  // the re-laid weights come from the launch before this one
+            uint32_t s = 0, ph = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            while (ok && next_tile(p, u, u_end, t)) {
+                for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
+                    int k_col = c0;  // column of (tap, channel block) in the re-laid weights: tap * C + c0
+                    for (int tap = 0; tap < p.kh * p.kw; tap++, k_col += p.C) {
+                        if (!mbar_wait(empty_a(s), ph ^ 1u)) {
+                            conv_timeout(p.status, 31);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(full_a(s), kABytes);
+                        tma_load_2d(sA + s * kABytes, &tmW0, full_a(s), k_col, t.m0);
+                        if (++s == w_stages) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
+        }
+    } else if (warp == 14) {
+        // input producer: one staging chunk per halo row and channel block
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            while (ok && next_tile(p, u, u_end, t)) {
+                const int hrows = t.rows + p.kh - 1;
+                for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
+                    for (int hr = 0; hr < hrows; hr++) {
+                        if (x_early > 0) {
+                            x_early--;  // issued before the block-wide synchronisation
+                        } else {
+                            if (!mbar_wait(empty_x(s), ph ^ 1u)) {
+                                conv_timeout(p.status, 37);
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_expect_tx(full_x(s), kChunkBytes);
+                            tma_load_4d(sX + s * kChunkBytes, &tmX, full_x(s), x0, t.oh0 - p.pad_h + hr, c0, t.n);
+                        }
+                        if (++s == n_chunks) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 200000) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // UMMA issuer
+        if (lane == 0) {
+            uint32_t lt = 0;
+            long long u = u_begin;
+            Tile t;
+            bool ok = true;
+            const uint64_t a_desc0 = make_smem_desc(sA, 16u, 1024u), h_desc0 = make_smem_desc(sH, 16u, 1024u);
+            uint32_t s = 0, ph = 0, hs = 0, hph = 0;
+            uint64_t a_desc = a_desc0;
+            while (ok && next_tile(p, u, u_end, t)) {
+                const uint32_t buf = lt & 1u, use = lt >> 1;
+                lt++;
+                if (!mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u)) {
+                    conv_timeout(p.status, 32);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t idesc = make_idesc(128, t.rows * 64, 1, 0, 0);
+                const uint32_t d_tmem = tmem_base + buf * 256u;
+                uint32_t acc = 0;
+                for (int cb = 0; cb < cblocks && ok; cb++) {
+                    if (!mbar_wait(full_h(hs), hph)) {
+                        conv_timeout(p.status, 36);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint64_t row_desc = h_desc0 + uint64_t(hs * (halo_bytes >> 4));
+                    for (int ky = 0; ky < p.kh && ok; ky++, row_desc += (64 * 128) >> 4) {
+                        uint64_t b_desc = row_desc;
+                        for (int kx = 0; kx < p.kw; kx++, b_desc += 128 >> 4) {
+                            if (!mbar_wait(full_a(s), ph)) {
+                                conv_timeout(p.status, 33);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            umma_f16_ss_x4<1>(d_tmem, a_desc, b_desc, idesc, acc, 2, 2);  // +32 bytes per 16-deep k-step
+                            acc = 1;
+                            umma_commit(empty_a(s));
+                            a_desc += kABytes >> 4;
+                            if (++s == w_stages) {
+                                s = 0;
+                                ph ^= 1u;
+                                a_desc = a_desc0;
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(empty_h(hs));
+                    if (++hs == uint32_t(kHaloSlots)) {
+                        hs = 0;
+                        hph ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(buf));
+            }
+        }
+    } else if (warp >= 10) {
+        // transposers: staging chunk [channel][pixel] -> halo slot rows [pixel slot][channel]
+        const int tw = warp - 10;
+        const int m = lane >> 3, r = lane & 7;  // this lane supplies row r of 8x8 block m to ldmatrix / stmatrix
+        const int shift = p.pad_w + x0;         // slot = staging pixel + shift (<= 0)
+        uint32_t xs = 0, xph = 0, hs = 0, hph = 0;
+        long long u = u_begin;
+        Tile t;
+        bool ok = true;
+        while (ok && next_tile(p, u, u_end, t)) {
+            const int hrows = t.rows + p.kh - 1;
+            for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
+                if (!mbar_wait(empty_h(hs), hph ^ 1u)) {
+                    if (lane == 0) conv_timeout(p.status, 35);
+                    ok = false;
+                    break;
+                }
+                const uint32_t slot = sH + hs * halo_bytes;
+                for (int hr = 0; hr < hrows; hr++) {
+                    if (!mbar_wait(full_x(xs), xph)) {
+                        if (lane == 0) conv_timeout(p.status, 38);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t chunk = sX + xs * kChunkBytes;
+                    // 16 units of (8 pixels x 32 channels) per chunk, four per warp: unit = (pixel group g, channel half hf)
+#pragma unroll
+                    for (int it = 0; it < 4; it++) {
+                        const int unit = tw * 4 + it;
+                        const int g = unit >> 1, hf = unit & 1;
+                        const int ch = hf * 32 + m * 8 + r;  // source row: a channel of the block
+                        uint32_t v[4];
+                        ldmatrix_x4_trans(chunk + uint32_t(ch) * 128u + (uint32_t(g ^ (ch & 7)) << 4), v);
+                        if constexpr (!IS_BF16) {  // fp16 input: the tensor cores run in the bf16 format of the re-laid weights
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const __half2 hv = *reinterpret_cast<const __half2*>(&v[i]);
+                                const __nv_bfloat162 bv = __float22bfloat162_rn(__half22float2(hv));
+                                v[i] = *reinterpret_cast<const uint32_t*>(&bv);
+                            }
+                        }
+                        // destination row: pixel slot of staging pixel 8g + r; 16-byte chunk = channel group hf*4 + m
+                        const int sl = g * 8 + r + shift;
+                        const uint32_t row = uint32_t(hr * 64 + sl);
+                        const uint32_t dst = sl >= 0 ? slot + row * 128u + ((uint32_t(hf * 4 + m) ^ (row & 7u)) << 4) : sDummy + uint32_t(lane) * 16u;
+                        stmatrix_x4(dst, v);
+                    }
+                    // slots right of what the box reaches (staging pixel 64 and up) hold zeros: the right padding
+                    for (int i = tw * 32 + lane; i < -shift * 8; i += 128) {
+                        const uint32_t row = uint32_t(hr * 64 + 64 + shift + (i >> 3));
+                        const uint32_t dst = slot + row * 128u + ((uint32_t(i & 7) ^ (row & 7u)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_x(xs));  // this warp has read its part of the chunk
+                    if (++xs == n_chunks) {
+                        xs = 0;
+                        xph ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                fence_proxy_async_smem();  // the tensor core reads these generic-proxy stores through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_h(hs));
+                if (++hs == uint32_t(kHaloSlots)) {
+                    hs = 0;
+                    hph ^= 1u;
+                }
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int wg = (warp - 2) >> 2;
+        uint32_t lt = 0;
+        long long u = u_begin;
+        Tile t;
+        const long long plane = (long long)p.Ho * p.Wo;
+        const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
+        while (next_tile(p, u, u_end, t)) {
+            const uint32_t buf = lt & 1u, use = lt >> 1;
+            lt++;
+            if (!mbar_wait(tfull_bar(buf), use & 1u)) {
+                if (lane == 0) conv_timeout(p.status, 34);
+                break;
+            }
+            tc_fence_after();
+            const int oc = t.m0 + q * 32 + lane;
+            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
+            const bool row_ok = oc < p.c_out;
+            const float bv = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.f;
+            // the two warps of a quadrant take alternate groups of 32 output pixels
+            int gi = 0;
+            for (int rr = 0; rr < t.rows; rr++) {
+                float* yrow = p.Y + ((long long)t.n * p.c_out + (row_ok ? oc : 0)) * plane + (long long)(t.oh0 + rr) * p.Wo;
+                for (int c = 0; c < p.Wo; c += 32, gi++) {
+                    if ((gi & 1) != wg) continue;
+                    const uint32_t col = uint32_t(rr * 64 + c);
+                    if (p.tma_out) {
+                        uint32_t r0[16], r1[16];
+                        tmem_ld_x16(t_addr + col, r0);
+                        tmem_ld_x16(t_addr + col + 16u, r1);
+                        if (lane == 0) tma_store_wait_read<0>();  // the previous store has finished reading the staging tile
+                        tmem_ld_wait();
+                        __syncwarp();
+#pragma unroll
+                        for (int sub = 0; sub < 2; sub++) {
+                            const uint32_t (&r)[16] = sub ? r1 : r0;
+#pragma unroll
+                            for (int v4 = 0; v4 < 4; v4++) {
+                                const int chunk = sub * 4 + v4;
+                                const uint32_t dst = stage_base + uint32_t(lane) * 128u + uint32_t((chunk ^ (lane & 7)) * 16);
+                                const uint32_t w0 = __float_as_uint(__uint_as_float(r[v4 * 4 + 0]) + bv);
+                                const uint32_t w1 = __float_as_uint(__uint_as_float(r[v4 * 4 + 1]) + bv);
+                                const uint32_t w2 = __float_as_uint(__uint_as_float(r[v4 * 4 + 2]) + bv);
+                                const uint32_t w3 = __float_as_uint(__uint_as_float(r[v4 * 4 + 3]) + bv);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && t.m0 + q * 32 < p.c_out) {
+                            tma_store_4d(&tmY, stage_base, c, t.oh0 + rr, t.m0 + q * 32, t.n);
+                            tma_store_commit();
+                        }
+                    } else {
+#pragma unroll
+                        for (int sub = 0; sub < 2; sub++) {
+                            uint32_t r[16];
+                            tmem_ld_x16(t_addr + col + uint32_t(sub * 16), r);
+                            tmem_ld_wait();
+                            if (!row_ok) continue;
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (c + sub * 16 + j < p.Wo) yrow[c + sub * 16 + j] = __uint_as_float(r[j]) + bv;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(buf));
+        }
+        if (p.tma_out && lane == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// W [oc][c][taps] -> bf16 [oc][taps][c] for the fused kernel. Every thread reads eight consecutive source elements
+// (one 16-byte load when the source allows it: the whole tensor is one trip to memory) and scatters them. Lets the
+// dependent launch start at once: that kernel waits for this grid (griddepcontrol.wait) only where it first reads the copy.
+template <typename TIn>
+__global__ void __launch_bounds__(256) conv_weights_kernel(const TIn* __restrict__ Wt, __nv_bfloat16* __restrict__ w_hi, int c_out, int C,
+                                                           int taps, int vec_ok) {
+    griddep_launch_dependents();
+    const long long total = (long long)c_out * C * taps;
+    const long long i0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (i0 >= total) return;
+    TIn v[8];
+    if (vec_ok && i0 + 8 <= total) {
+        *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(Wt + i0));
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = i0 + e < total ? Wt[i0 + e] : TIn(0.f);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const long long i = i0 + e;  // source index ((oc * C + c) * taps + tap)
+        if (i < total) {
+            const int tap = int(i % taps);
+            const long long oc_c = i / taps;
+            const int c = int(oc_c % C);
+            const long long oc = oc_c / C;
+            w_hi[(oc * taps + tap) * C + c] = __float2bfloat16_rn(to_float(v[e]));
+        }
+    }
+}
+
 // X [N][C][HW] -> hi (and lo) [N][HW][C] as bf16, and the weights in the same launch (the blocks of the last
 // grid row, blockIdx.y == C / 64). A block moves PX pixels x 64 channels through shared memory as 32-bit
 // words holding a channel pair: reads walk pixels (coalesced in NCHW), writes walk channels, so every
@@ -661,6 +1086,79 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
 
 bool g_conv_attr[16] = {false};
 bool g_halo_attr[16] = {false};
+bool g_fused_attr[16][2] = {};
+
+// The fused path: weights re-laid by a small launch, then conv_nchw_kernel on the NCHW input in place.
+template <bool IS_BF16>
+int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const void* X, const void* Wt, float* Y, bool tma_out) {
+    using TIn = typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type;
+    const int64_t taps = q.kh * q.kw, Kt = taps * q.C;
+    const size_t w_elems = size_t(q.c_out) * Kt;
+    void* ww;
+    DOCC_TRY(get_workspace(ctx, 1, w_elems * 2 + 256, &ww));
+    __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
+    CUtensorMap tm_w, tm_x, tm_y;
+    memset(&tm_y, 0, sizeof(tm_y));
+    {
+        const uint64_t wd[2] = {uint64_t(Kt), uint64_t(q.c_out)};
+        const uint64_t ws[1] = {uint64_t(Kt) * 2};
+        const uint32_t wb[2] = {64, 128};
+        DOCC_TRY(encode_tmap_16bit(&tm_w, w_hi, 2, wd, ws, wb));
+        // the input as it lies in memory: pixels, rows, channels, images; one box = one row of 64 channels
+        const uint64_t xd[4] = {uint64_t(q.W), uint64_t(q.H), uint64_t(q.C), uint64_t(q.N)};
+        const uint64_t xs[3] = {uint64_t(q.W) * 2, uint64_t(q.H * q.W) * 2, uint64_t(q.H * q.W) * q.C * 2};
+        const uint32_t xb[4] = {64, 1, 64, 1};
+        DOCC_TRY(encode_tmap_16bit(&tm_x, X, 4, xd, xs, xb));
+    }
+    if (tma_out) {
+        const uint64_t yd[4] = {uint64_t(q.Wo), uint64_t(q.Ho), uint64_t(q.c_out), uint64_t(q.N)};
+        const uint64_t ys[3] = {uint64_t(q.Wo) * 4, uint64_t(q.Ho * q.Wo) * 4, uint64_t(q.Ho * q.Wo) * q.c_out * 4};
+        const uint32_t yb[4] = {32, 1, 32, 1};
+        DOCC_TRY(encode_tmap(&tm_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, CU_TENSOR_MAP_SWIZZLE_128B, Y, 4, yd, ys, yb));
+    }
+    // shared memory: two halo slots, eight epilogue staging tiles, then the two rings share what is left
+    const size_t halo_total = size_t(kHaloSlots) * size_t(p.r_max + p.kh - 1) * 8192;
+    const size_t fixed = 8 * 4096 + 512 + 1024 + 512;
+    const size_t rings = 227 * 1024 - halo_total - fixed;
+    int x_chunks = 4;
+    int w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
+    if (w_stages < 3) {  // tall filters leave little room: a shallower input ring
+        x_chunks = 2;
+        w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
+    }
+    if (w_stages > kMaxWStages) w_stages = kMaxWStages;
+    if (w_stages < 2) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: filter too tall for the fused kernel");
+    p.w_stages = w_stages;
+    p.x_chunks = x_chunks;
+    const size_t smem = halo_total + size_t(w_stages) * kABytes + size_t(x_chunks) * kChunkBytes + fixed;
+    auto kern = conv_nchw_kernel<IS_BF16>;
+    if (!g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0] = true;
+    }
+    {
+        const long long wblocks = ceil_div((long long)w_elems, 256 * 8);
+        if (wblocks > 0x7fffffff) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: weight tensor too large");
+        const int vec_ok = reinterpret_cast<uintptr_t>(Wt) % 16 == 0 ? 1 : 0;
+        conv_weights_kernel<TIn><<<unsigned(wblocks), 256, 0, ctx->stream>>>(static_cast<const TIn*>(Wt), w_hi, int(q.c_out), int(q.C), int(taps), vec_ok);
+        DOCC_TRY(after_launch(ctx, "conv_weights_kernel"));
+    }
+    long long grid = ceil_div(p.total_units, p.r_max);
+    if (grid > ctx->sm_count) grid = ctx->sm_count;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DOCC_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, p));
+    return after_launch(ctx, "conv_nchw_kernel");
+}
 
 }  // namespace
 
@@ -672,6 +1170,29 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     const bool split = q.prec_in == DOCC_B200_PREC_S;
     const int planes = split ? 2 : 1;
     const int64_t HW = q.H * q.W, taps = q.kh * q.kw, Kt = taps * q.C;
+    {
+        // 16-bit NCHW inputs of narrow images go through the kernel that reads them in place (TMA rules: rows of a
+        // multiple of 16 bytes on a 16-byte aligned base; one 64-pixel box per row has to reach every column a tap reads)
+        const int fused_rmax = int(10 - q.kh) < 4 ? int(10 - q.kh) : 4;
+        static const int fused_mode = [] { const char* e = getenv("DOCC_B200_CONV_FUSED"); return e ? atoi(e) : 1; }();
+        const bool reach = q.pad_w == 0 ? q.W <= 64 : (q.pad_w <= 8 && q.W <= 56);
+        if (fused_mode && !split && q.W % 8 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && q.Wo + q.kw - 1 <= 64 && reach &&
+            q.pad_w >= 0 && fused_rmax >= 1) {
+            ConvKernelParams p;
+            memset(&p, 0, sizeof(p));
+            p.N = int(q.N); p.C = int(q.C); p.H = int(q.H); p.W = int(q.W); p.c_out = int(q.c_out);
+            p.kh = int(q.kh); p.kw = int(q.kw); p.pad_h = int(q.pad_h); p.pad_w = int(q.pad_w); p.Ho = int(q.Ho); p.Wo = int(q.Wo);
+            p.npass = 1;
+            p.r_max = fused_rmax;
+            p.tiles_m = int(ceil_div(q.c_out, 128));
+            p.total_units = (long long)p.tiles_m * q.N * q.Ho;
+            const bool tma_out = q.Wo % 4 == 0 && reinterpret_cast<uintptr_t>(Y) % 16 == 0;
+            p.tma_out = tma_out ? 1 : 0;
+            p.bias = bias; p.Y = Y; p.status = ctx->status_dev;
+            return q.prec_in == DOCC_B200_PREC_B ? launch_fused<true>(ctx, q, p, X, Wt, Y, tma_out)
+                                                 : launch_fused<false>(ctx, q, p, X, Wt, Y, tma_out);
+        }
+    }
     const size_t x_elems = size_t(q.N) * HW * q.C, w_elems = size_t(q.c_out) * Kt;
     void *wx, *ww;
     DOCC_TRY(get_workspace(ctx, 0, x_elems * planes * 2, &wx));
@@ -779,3 +1300,4 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
 }
 
 }  // namespace docc_b200
+

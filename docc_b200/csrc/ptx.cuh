@@ -81,6 +81,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
     return true;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream still runs. griddep_wait() blocks until that kernel has completed and its memory operations are visible (a
+// no-op without the attribute); griddep_launch_dependents() in the earlier kernel lets the later one start at once.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

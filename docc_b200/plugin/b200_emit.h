@@ -28,12 +28,18 @@ inline bool debug_checks_enabled() {
 template <class Stream> void emit_include(Stream& globals) { globals << "#include <docc_b200/rt.h>\n"; }
 
 // Unchecked by default (as docc); with checks: print and exit like check_cuda_kernel_launch_errors.
-template <class Stream> void emit_call(Stream& s, const std::string& name, const std::string& args, bool checked) {
+// `locals` (optional) are declarations the arguments refer to; they and the call then share one scope.
+template <class Stream>
+void emit_call(Stream& s, const std::string& name, const std::string& args, bool checked, const std::string& locals = "") {
     if (!checked) {
-        s << name << "(" << args << ");\n";
+        if (locals.empty()) {
+            s << name << "(" << args << ");\n";
+        } else {
+            s << "{\n" << locals << "    " << name << "(" << args << ");\n}\n";
+        }
         return;
     }
-    s << "{\n";
+    s << "{\n" << locals;
     s << "    int __docc_b200_st = " << name << "(" << args << ");\n";
     s << "    if (__docc_b200_st != 0) {\n";
     s << "        fprintf(stderr, \"" << name << ": %s (%s)\\n\", docc_b200_strerror(__docc_b200_st), docc_b200_last_error());\n";
@@ -47,8 +53,9 @@ inline std::string join(const std::vector<std::string>& v) {
     for (size_t i = 0; i < v.size(); i++) out += (i ? ", " : "") + v[i];
     return out;
 }
-inline std::string i64_array(const std::vector<std::string>& v) {
-    return "(const int64_t[]){" + (v.empty() ? std::string("0") : join(v)) + "}";
+// A named local array of symbolic extents (a compound literal with run-time elements is not valid C++).
+inline std::string i64_local(const std::string& name, const std::vector<std::string>& v) {
+    return "    const int64_t " + name + "[] = {" + (v.empty() ? std::string("0") : join(v)) + "};\n";
 }
 
 // GEMMNode -> docc_b200_gemm. precision is BLAS_Precision's char, layout / trans are the enum values
@@ -80,17 +87,17 @@ template <class Stream>
 void emit_softmax(Stream& s, char precision, const std::vector<std::string>& shape, const std::vector<std::string>& axes,
                   bool with_transfers, bool checked) {
     std::ostringstream a;
-    a << "'" << precision << "', " << shape.size() << ", " << i64_array(shape) << ", " << axes.size() << ", " << i64_array(axes)
-      << ", X, Y, " << (with_transfers ? 1 : 0);
-    emit_call(s, "docc_b200_softmax", a.str(), checked);
+    a << "'" << precision << "', " << shape.size() << ", __docc_b200_shape, " << axes.size() << ", __docc_b200_axes, X, Y, "
+      << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_softmax", a.str(), checked, i64_local("__docc_b200_shape", shape) + i64_local("__docc_b200_axes", axes));
 }
 template <class Stream>
 void emit_reduce(Stream& s, int op, char precision, const std::vector<std::string>& shape, const std::vector<std::string>& axes,
                  bool with_transfers, bool checked) {
     std::ostringstream a;
-    a << op << ", '" << precision << "', " << shape.size() << ", " << i64_array(shape) << ", " << axes.size() << ", "
-      << i64_array(axes) << ", X, Y, " << (with_transfers ? 1 : 0);
-    emit_call(s, "docc_b200_reduce", a.str(), checked);
+    a << op << ", '" << precision << "', " << shape.size() << ", __docc_b200_shape, " << axes.size() << ", __docc_b200_axes, X, Y, "
+      << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_reduce", a.str(), checked, i64_local("__docc_b200_shape", shape) + i64_local("__docc_b200_axes", axes));
 }
 
 // ConvNode -> docc_b200_conv (connectors X, W, [B] -> Y). x_shape = [N, C_in, D0..]; pads = begins then ends.
@@ -100,10 +107,76 @@ void emit_conv(Stream& s, char precision, const std::vector<std::string>& x_shap
                const std::vector<std::string>& dilations, const std::string& c_out, const std::string& group, bool has_bias,
                bool with_transfers, bool checked) {
     std::ostringstream a;
-    a << "'" << precision << "', '" << precision << "', " << kernel_shape.size() << ", " << i64_array(x_shape) << ", "
-      << i64_array(kernel_shape) << ", " << i64_array(strides) << ", " << i64_array(pads) << ", " << i64_array(dilations) << ", "
-      << c_out << ", " << group << ", X, W, " << (has_bias ? "B" : "NULL") << ", Y, " << (with_transfers ? 1 : 0);
-    emit_call(s, "docc_b200_conv", a.str(), checked);
+    a << "'" << precision << "', '" << precision << "', " << kernel_shape.size()
+      << ", __docc_b200_x, __docc_b200_k, __docc_b200_strides, __docc_b200_pads, __docc_b200_dil, " << c_out << ", " << group
+      << ", X, W, " << (has_bias ? "B" : "NULL") << ", Y, " << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_conv", a.str(), checked,
+              i64_local("__docc_b200_x", x_shape) + i64_local("__docc_b200_k", kernel_shape) + i64_local("__docc_b200_strides", strides) +
+                  i64_local("__docc_b200_pads", pads) + i64_local("__docc_b200_dil", dilations));
+}
+
+// AttentionNode -> docc_b200_attention (connectors Q, K, V -> O; contiguous [B,H,S,D] operands, so all stride
+// arguments are NULL). A scale <= 0 asks for 1/sqrt(head_dim), computed in the generated code.
+template <class Stream>
+void emit_attention(Stream& s, char precision, const std::string& batch, const std::string& heads, const std::string& seq_q,
+                    const std::string& seq_kv, const std::string& head_dim, double scale, bool causal, bool with_transfers,
+                    bool checked) {
+    std::ostringstream a;
+    a.precision(17);
+    a << "'" << precision << "', " << batch << ", " << heads << ", " << seq_q << ", " << seq_kv << ", " << head_dim << ", ";
+    if (scale > 0) a << "(float)" << scale;
+    else a << "1.0f / sqrtf((float)(" << head_dim << "))";
+    a << ", " << (causal ? 1 : 0) << ", Q, NULL, K, NULL, V, NULL, O, NULL, " << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_attention", a.str(), checked);
+}
+
+// LayerNormNode -> docc_b200_layernorm (connectors X, [G, B] -> Y; rows = product of the leading dimensions).
+template <class Stream>
+void emit_layernorm(Stream& s, char precision, const std::string& rows, const std::string& cols, double eps, bool affine,
+                    bool with_transfers, bool checked) {
+    std::ostringstream a;
+    a.precision(17);
+    a << "'" << precision << "', " << rows << ", " << cols << ", X, " << (affine ? "G, B" : "NULL, NULL") << ", " << eps << ", Y, "
+      << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_layernorm", a.str(), checked);
+}
+
+// ElementWiseUnaryNode (Exp, Erf, Tanh, Sqrt, Sigmoid, ReLU, Abs; connectors X -> Y, elementwise_node.cpp:86-200)
+// -> docc_b200_bias_act with the matching activation code, scale 1, no bias, no residual. `count` is the product of
+// the node's shape; the call sees the tensor as one row.
+template <class Stream>
+void emit_unary(Stream& s, char precision, int act, const std::string& count, bool with_transfers, bool checked) {
+    std::ostringstream a;
+    a << "'" << precision << "', 1, " << count << ", X, 1.0f, NULL, " << act << ", NULL, Y, " << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_bias_act", a.str(), checked);
+}
+
+// ElementWiseBinaryNode (Add, Sub, Mul, Div, Maximum, Minimum; connectors A, B -> C, elementwise_node.cpp:202-339)
+// -> docc_b200_binary.
+template <class Stream>
+void emit_binary(Stream& s, int op, char precision, const std::string& count, bool with_transfers, bool checked) {
+    std::ostringstream a;
+    a << op << ", '" << precision << "', " << count << ", A, B, C, " << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_binary", a.str(), checked);
+}
+
+// CastNode (connectors X -> Y) -> docc_b200_cast.
+template <class Stream>
+void emit_cast(Stream& s, char precision_in, char precision_out, const std::string& count, bool with_transfers, bool checked) {
+    std::ostringstream a;
+    a << "'" << precision_in << "', '" << precision_out << "', " << count << ", X, Y, " << (with_transfers ? 1 : 0);
+    emit_call(s, "docc_b200_cast", a.str(), checked);
+}
+
+// One CUDADataOffloadingNode (cuda_data_offloading_node.cpp:139-173) in the order its dispatcher uses: allocation
+// first, then the copy, then the release. `dst` / `src` are the node's output(0) / input(0) connector names.
+template <class Stream>
+void emit_offload(Stream& s, bool alloc, bool h2d, bool d2h, bool free_, const std::string& dst, const std::string& src,
+                  const std::string& bytes, bool checked) {
+    if (alloc) emit_call(s, "docc_b200_malloc", "(void**)&" + dst + ", " + bytes, checked);
+    if (h2d) emit_call(s, "docc_b200_h2d", dst + ", " + src + ", " + bytes, checked);
+    else if (d2h) emit_call(s, "docc_b200_d2h", dst + ", " + src + ", " + bytes, checked);
+    if (free_) emit_call(s, "docc_b200_free", src, checked);
 }
 
 // CUDADataOffloadingNode lifecycle -> pool / transfer calls (cuda_data_offloading_node.cpp:149-172).

@@ -322,6 +322,43 @@ def test_conv_tensor_core_geometries(rt, n, c, h, w, co, k, pad):
     assert relerr(got16, ref16) <= TOL_16
 
 
+# 16-bit NCHW inputs of narrow images whose rows are a multiple of 16 bytes are read in place by the fused kernel (TMA
+# staging, transposer warps fill the tensor-core layout); other widths and unaligned bases keep the path through the
+# re-laid copy. Both must agree with the oracle, for bf16 and fp16, with tiles that start and end inside an image and
+# images whose rows span CTAs.
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n,c,h,w,co,k,pad", [
+    (3, 64, 56, 56, 128, 3, 1),   # config 3 geometry, three images
+    (5, 64, 13, 22, 40, 3, 1),    # few rows per image: tiles cut at image ends
+    (2, 128, 17, 31, 64, 3, 1),   # odd width: re-laid copy
+    (1, 64, 30, 58, 64, 3, 0),    # no padding
+    (2, 64, 9, 16, 64, 3, 2),     # padding wider than the filter needs
+    (160, 64, 6, 8, 16, 3, 1),    # many small images: more tiles than SMs
+    (2, 128, 20, 48, 130, 3, 1),  # two channel blocks, two channel tiles, columns 48..55 of the box outside the image
+    (1, 64, 9, 64, 64, 1, 0),     # no padding, full-width box
+    (2, 64, 14, 40, 48, 5, 2),    # 5x5 filter
+    (1, 64, 12, 24, 64, 7, 3),    # 7x7 filter: shallow rings
+    (1, 64, 30, 56, 128, 3, 1),
+])
+def test_conv_16bit_nchw_in_place(rt, dtype, n, c, h, w, co, k, pad):
+    torch.manual_seed(11)
+    x = torch.randn(n, c, h, w).to(dtype)
+    wt = (torch.randn(co, c, k, k) / (c * k * k) ** 0.5).to(dtype)
+    b = torch.randn(co)
+    pads = [pad, pad, pad, pad]
+    # the tensor cores run both 16-bit types in bf16, so the fp16 reference rounds its operands the same way
+    xr, wr = (t_.bfloat16().float().numpy() for t_ in (x, wt))
+    ref = oracle.conv(xr, wr, b.numpy(), pads=pads)
+    got = host(ops.conv(x.cuda(), wt.cuda(), b.cuda(), pads=pads))
+    assert got.shape == ref.shape
+    assert relerr(got, ref) <= (1e-5 if dtype == torch.bfloat16 else TOL_16)
+    # an input that starts 2 bytes off a 4-byte boundary cannot be read in pixel pairs: same result through the copy
+    flat = torch.empty(x.numel() + 1, dtype=dtype, device="cuda")
+    flat[1:] = x.cuda().reshape(-1)
+    got_off = host(ops.conv(flat[1:].view(n, c, h, w), wt.cuda(), b.cuda(), pads=pads))
+    assert relerr(got_off, ref) <= (1e-5 if dtype == torch.bfloat16 else TOL_16)
+
+
 def test_conv_linearity_full_config3(rt):
     # size-independent property at the full config: conv(x1 + x2) == conv(x1) + conv(x2)
     torch.manual_seed(2)
