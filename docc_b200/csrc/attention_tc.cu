@@ -140,6 +140,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // everything before this point touches no global memory: under programmatic stream serialization it overlaps
+    // the tail of the kernel launched before this one
+    griddep_wait();
+    griddep_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -437,6 +441,10 @@ __global__ void __launch_bounds__(320, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // everything before this point touches no global memory: under programmatic stream serialization it overlaps
+    // the tail of the kernel launched before this one
+    griddep_wait();
+    griddep_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -815,6 +823,10 @@ __global__ void __launch_bounds__(320, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // everything before this point touches no global memory: under programmatic stream serialization it overlaps
+    // the tail of the kernel launched before this one
+    griddep_wait();
+    griddep_launch_dependents();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -1175,7 +1187,7 @@ int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, const AttnK
         g_attr2_done[ctx->device & 15][slot] = true;
     }
     const int64_t grid = p.B * p.H * ((kp.n_qtiles + 1) / 2);
-    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
+    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(grid)), dim3(320), smem, ctx->stream, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp));
     return after_launch(ctx, "attention_tc2_kernel");
 }
 
@@ -1197,7 +1209,7 @@ int launch2p(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, AttnKernel
     const int64_t items = p.B * p.H * ((kp.n_qtiles + 1) / 2);
     kp.n_items = int(items);
     const int64_t grid = items < ctx->sm_count ? items : ctx->sm_count;
-    kern<<<unsigned(grid), 320, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp);
+    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(grid)), dim3(320), smem, ctx->stream, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], kp));
     return after_launch(ctx, "attention_tc2p_kernel");
 }
 
@@ -1205,6 +1217,8 @@ int launch2p(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, AttnKernel
 __global__ void __launch_bounds__(256) split_heads_kernel(const float* __restrict__ X, long long sb, long long sh, long long ss,
                                                           int H, int S, int D, long long total4, __nv_bfloat16* __restrict__ hi,
                                                           __nv_bfloat16* __restrict__ lo) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int d4 = D / 4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
         const int dq = int(i % d4);
@@ -1237,7 +1251,7 @@ int launch(Ctx* ctx, const AttnProblem& p, const CUtensorMap& tq, const CUtensor
         g_attr_done[ctx->device & 15][slot] = true;
     }
     const int64_t grid = p.B * p.H * kp.n_qtiles;
-    kern<<<unsigned(grid), kAttnThreads, smem, ctx->stream>>>(tq, tk, tv, kp);
+    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(grid)), dim3(kAttnThreads), smem, ctx->stream, tq, tk, tv, kp));
     return after_launch(ctx, "attention_tc_kernel");
 }
 
@@ -1320,8 +1334,9 @@ int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* 
         const long long total4 = (long long)(p.B * p.H * seq[i] * p.D / 4);
         long long blocks = (total4 + 255) / 256;
         if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
-        split_heads_kernel<<<unsigned(blocks), 256, 0, ctx->stream>>>(static_cast<const float*>(src[i]), str[i][0], str[i][1], str[i][2],
-                                                                      int(p.H), int(seq[i]), int(p.D), total4, planes[i], planes[3 + i]);
+        DOCC_CUDA_TRY(launch_pdl(split_heads_kernel, dim3(unsigned(blocks)), dim3(256), 0, ctx->stream, static_cast<const float*>(src[i]),
+                                 (long long)str[i][0], (long long)str[i][1], (long long)str[i][2], int(p.H), int(seq[i]), int(p.D), total4,
+                                 planes[i], planes[3 + i]));
         DOCC_TRY(after_launch(ctx, "split_heads_kernel"));
     }
     CUtensorMap maps[6];

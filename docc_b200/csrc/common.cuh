@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <utility>
 
 #include "docc_b200/rt.h"
 
@@ -101,5 +102,26 @@ struct TempBuffers {
 };
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Launch with programmatic stream serialization: the kernel may become resident while the kernel before it in the
+// stream is still running, so its launch latency and set-up (barrier initialisation, tensor-memory allocation,
+// descriptor prefetch) disappear behind that kernel's tail. Only for kernels that execute griddepcontrol.wait
+// (ptx::griddep_wait) before their first access to global memory; the wait returns once the earlier kernel has
+// completed and its writes are visible, so no data dependence is relaxed.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 }  // namespace docc_b200

@@ -13,10 +13,17 @@ namespace {
 // One warp per row while a row fits in registers (cols <= 32*VPT*VEC), else block per row.
 // Two-pass statistics in registers: mean, then sum((x-mean)^2) — the form torch lowers to and
 // the numerically safe one; population variance as in StdNode (std_node.cpp:147-222).
+// Both LayerNorm kernels run under programmatic stream serialization: nothing is read before the wait.
+__device__ __forceinline__ void griddep_wait_all() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 template <typename T, int VPT, int TPR, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) layernorm_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
                                                           const float* __restrict__ beta, float eps, T* __restrict__ Y,
                                                           int64_t rows, int64_t cols) {
+    griddep_wait_all();
     constexpr int VEC = 16 / sizeof(T);
     using P = Pack<T, VEC>;
     constexpr int RPB = BLOCK / TPR;
@@ -100,6 +107,87 @@ __global__ void __launch_bounds__(BLOCK) layernorm_kernel(const T* __restrict__ 
     }
 }
 
+// Rows that fit one warp's registers, many rows per warp: every warp walks rows w, w + W, w + 2W, ... (W = warps in the
+// grid) with its slice of gamma / beta held in registers for the whole walk and the next row's loads issued before the
+// current row is reduced, so that loads are in flight all the time. Against one row group per block this removes the
+// per-row parameter loads (16 of the 24 memory instructions a thread issued per bf16 row of 1024) and the
+// load -> reduce -> store -> exit bubbles of short-lived blocks.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256, 2) layernorm_warp_rows_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
+                                                                     const float* __restrict__ beta, float eps, T* __restrict__ Y,
+                                                                     int64_t rows, int64_t cols) {
+    griddep_wait_all();
+    constexpr int VEC = 16 / sizeof(T);
+    using P = Pack<T, VEC>;
+    const int lane = threadIdx.x & 31;
+    const int64_t packs = cols / VEC;
+    const int64_t warps = int64_t(gridDim.x) * 8;
+    int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float gm[VPT][VEC], bt[VPT][VEC];
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        const int64_t p = int64_t(i) * 32 + lane;
+#pragma unroll
+        for (int q4 = 0; q4 < VEC / 4; q4++) {
+            const bool in = p < packs;
+            const float4 g4 = (gamma && in) ? __ldg(reinterpret_cast<const float4*>(gamma + p * VEC) + q4) : make_float4(1.f, 1.f, 1.f, 1.f);
+            const float4 b4 = (beta && in) ? __ldg(reinterpret_cast<const float4*>(beta + p * VEC) + q4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            gm[i][q4 * 4 + 0] = g4.x; gm[i][q4 * 4 + 1] = g4.y; gm[i][q4 * 4 + 2] = g4.z; gm[i][q4 * 4 + 3] = g4.w;
+            bt[i][q4 * 4 + 0] = b4.x; bt[i][q4 * 4 + 1] = b4.y; bt[i][q4 * 4 + 2] = b4.z; bt[i][q4 * 4 + 3] = b4.w;
+        }
+    }
+    P nxt[VPT];
+    auto load_row = [&](int64_t r) {
+        const P* xr = reinterpret_cast<const P*>(X + r * cols);
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+            const int64_t p = int64_t(i) * 32 + lane;
+            if (p < packs) nxt[i] = load_pack(xr + p);
+        }
+    };
+    load_row(row);
+    const float inv_cols = 1.f / float(cols);
+    for (; row < rows; row += warps) {
+        // the row stays in its storage type (half the registers for 16-bit rows); conversions are repeated per pass
+        P cur[VPT];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+            cur[i] = nxt[i];
+            if (int64_t(i) * 32 + lane < packs) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) s += to_float(cur[i].v[e]);
+            }
+        }
+        if (row + warps < rows) load_row(row + warps);  // in flight during the reductions and the stores below
+        const float mean = warp_sum_f(s) * inv_cols;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+            if (int64_t(i) * 32 + lane < packs) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) {
+                    const float d = to_float(cur[i].v[e]) - mean;
+                    q += d * d;
+                }
+            }
+        }
+        const float rstd = rsqrtf(warp_sum_f(q) * inv_cols + eps);
+        P* yr = reinterpret_cast<P*>(Y + row * cols);
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+            const int64_t p = int64_t(i) * 32 + lane;
+            if (p < packs) {
+                P pk;
+#pragma unroll
+                for (int e = 0; e < VEC; e++) pk.v[e] = from_float<T>((to_float(cur[i].v[e]) - mean) * rstd * gm[i][e] + bt[i][e]);
+                store_pack(yr + p, pk);
+            }
+        }
+    }
+}
+
 // Any cols / alignment: block per row, three passes over global memory.
 template <typename T>
 __global__ void __launch_bounds__(256) layernorm_generic_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
@@ -123,6 +211,15 @@ __global__ void __launch_bounds__(256) layernorm_generic_kernel(const T* __restr
     }
 }
 
+template <typename T, int VPT>
+int launch_ln_warp_rows(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
+    // two resident blocks of eight warps per SM; fewer when there are not that many rows
+    int64_t blocks = ceil_div(rows, 8);
+    if (blocks > int64_t(ctx->sm_count) * 2) blocks = int64_t(ctx->sm_count) * 2;
+    DOCC_CUDA_TRY(launch_pdl(layernorm_warp_rows_kernel<T, VPT>, dim3(unsigned(blocks)), dim3(256), 0, ctx->stream, X, g, b, eps, Y, rows, cols));
+    return after_launch(ctx, "layernorm_warp_rows_kernel");
+}
+
 template <typename T, int VPT, int TPR>
 int launch_ln(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
     constexpr int BLOCK = TPR > 256 ? TPR : 256;
@@ -130,7 +227,8 @@ int launch_ln(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T
     // one row group per block (the block scheduler balances the SMs; a resident-size grid with a stride loop leaves SMs
     // idle in the last partial round of groups)
     const int64_t cap = 0x7fffffff;
-    layernorm_kernel<T, VPT, TPR, BLOCK><<<int(groups < cap ? groups : cap), BLOCK, 0, ctx->stream>>>(X, g, b, eps, Y, rows, cols);
+    DOCC_CUDA_TRY(launch_pdl(layernorm_kernel<T, VPT, TPR, BLOCK>, dim3(unsigned(groups < cap ? groups : cap)), dim3(BLOCK), 0, ctx->stream,
+                             X, g, b, eps, Y, rows, cols));
     return after_launch(ctx, "layernorm_kernel");
 }
 
@@ -144,7 +242,11 @@ int layernorm_device(Ctx* ctx, int64_t rows, int64_t cols, const T* X, const flo
     if (aligned && packs <= 2048) {
         if (packs <= 32) return launch_ln<T, 1, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 64) return launch_ln<T, 2, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
-        if (packs <= 128) return launch_ln<T, 4, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
+        if (packs <= 128) {
+            // enough rows for every warp of a resident-size grid to amortise its parameter registers over a few rows
+            if (rows >= int64_t(ctx->sm_count) * 64) return launch_ln_warp_rows<T, 4>(ctx, X, g, b, float(eps), Y, rows, cols);
+            return launch_ln<T, 4, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
+        }
         if (packs <= 256) return launch_ln<T, 8, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 512) return launch_ln<T, 4, 128>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 1024) return launch_ln<T, 8, 128>(ctx, X, g, b, float(eps), Y, rows, cols);

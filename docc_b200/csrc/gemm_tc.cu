@@ -83,9 +83,10 @@ __device__ __forceinline__ void report_timeout(DeviceStatus* st, unsigned where)
 // Epilogue arithmetic for 16 consecutive columns of one accumulator row:
 // v = act(alpha*acc + beta*C + bias) + residual. Columns at or beyond N are left untouched.
 // ACT is the activation code, or -1 to select it at run time (rare codes only).
+// `pre`: the residual's 16 columns were fetched by the caller (`res_pre`, 16-byte vectors) instead of being read here.
 template <typename OutT, int ACT>
 __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const uint32_t (&r)[16], long long row, int col0, int b,
-                                                bool row_ok, float (&v)[16]) {
+                                                bool row_ok, float (&v)[16], bool pre, const uint4 (&res_pre)[16 / (16 / int(sizeof(OutT)))]) {
     int ncols = p.N - col0 < 16 ? p.N - col0 : 16;
     if (ncols < 0 || !row_ok) ncols = 0;
 #pragma unroll
@@ -126,7 +127,10 @@ __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const u
     }
     if constexpr (ACT == DOCC_B200_ACT_GELU_ERF) {
 #pragma unroll
-        for (int j = 0; j < 16; j++) v[j] = 0.5f * v[j] * (1.0f + erf_fast(v[j] * 0.70710678118654752440f));
+        for (int j = 0; j < 16; j++) {
+            if constexpr (sizeof(OutT) == 2) v[j] = gelu_erf_16bit(v[j]);
+            else v[j] = 0.5f * v[j] * (1.0f + erf_fast(v[j] * 0.70710678118654752440f));
+        }
     } else if constexpr (ACT == DOCC_B200_ACT_RELU) {
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] = fmaxf(v[j], 0.f);
@@ -134,7 +138,14 @@ __device__ __forceinline__ void epilogue_values(const TcKernelParams& p, const u
 #pragma unroll
         for (int j = 0; j < 16; j++) v[j] = apply_act_fast(p.act, v[j]);
     }
-    if (p.residual && ncols > 0) {
+    if (pre) {
+#pragma unroll
+        for (int q = 0; q < 16 / EPV; q++) {
+            const Pack<OutT, EPV> c = *reinterpret_cast<const Pack<OutT, EPV>*>(&res_pre[q]);
+#pragma unroll
+            for (int e = 0; e < EPV; e++) v[q * EPV + e] += to_float(c.v[e]);
+        }
+    } else if (p.residual && ncols > 0) {
         const OutT* rrow = static_cast<const OutT*>(p.residual) + b * p.res_bs + row * p.ldr + col0;
         if (full && p.vec_res) {
 #pragma unroll
@@ -192,16 +203,52 @@ __device__ __forceinline__ void epilogue_stage(uint32_t stage_base, int lane, in
     }
 }
 
+// Fetches a 32-row x 128-byte residual tile with coalesced requests (all eight in flight together) and parks it in the
+// warp's staging tile in the swizzled layout, once the previous TMA store has finished reading that tile. Kept out of
+// line: inlined, its eight vectors push the epilogue's register allocation over the limit.
+template <typename OutT>
+__device__ __noinline__ void stage_residual_tile(const OutT* rbase, long long ldr, uint32_t stage_base, int lane) {
+    constexpr int EPV = 16 / int(sizeof(OutT));
+    uint4 rt[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int id = i * 32 + lane;  // 16-byte chunk (id & 7) of tile row (id >> 3)
+        rt[i] = __ldg(reinterpret_cast<const uint4*>(rbase + (long long)(id >> 3) * ldr + (id & 7) * EPV));
+    }
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int id = i * 32 + lane;
+        const int rr = id >> 3, ch = id & 7;
+        const uint32_t dst = stage_base + uint32_t(rr) * 128u + uint32_t((ch ^ (rr & 7)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(rt[i].x), "r"(rt[i].y), "r"(rt[i].z), "r"(rt[i].w) : "memory");
+    }
+    __syncwarp();
+}
+
 template <typename OutT, int ACT>
 __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUtensorMap* tm_out, uint32_t stage_base, uint32_t t_addr,
                                               int c_begin, int c_end, long long row, int row0, int n0, int b, int lane) {
     const bool row_ok = row < p.M;
     if (p.tma_out) {
         constexpr int BOX = 128 / sizeof(OutT);  // columns per 128-byte staging row
+        constexpr int EPV = 16 / int(sizeof(OutT));  // elements per 16-byte vector
+        constexpr int CHUNKS = 16 / EPV;             // vectors per 16 columns
         for (int c0 = c_begin; c0 < c_end; c0 += BOX) {
-            // the previous TMA store must have finished reading the staging tile
-            if (lane == 0) tma_store_wait_read<0>();
-            __syncwarp();
+            // Residual: a thread owns an accumulator row, so reading "its" residual means 32 lanes touching 32 different
+            // lines, 16 bytes at a time. When the whole 32 x 128-byte tile is in range the warp fetches it the other way
+            // round instead, as eight coalesced 512-byte requests that are all in flight together, parks it in the staging
+            // tile (same swizzled layout the result will have) and every lane then picks its row up from shared memory.
+            // (16-bit results with the plain or the GELU / ReLU epilogue: the other instantiations have no registers to spare)
+            const bool res_tile = sizeof(OutT) == 2 && ACT >= 0 && p.residual != nullptr && p.vec_res && row0 + 32 <= p.M && n0 + c0 + BOX <= p.N;
+            if (res_tile) {
+                stage_residual_tile<OutT>(static_cast<const OutT*>(p.residual) + b * p.res_bs + (long long)row0 * p.ldr + n0 + c0, p.ldr, stage_base, lane);
+            } else {
+                // the previous TMA store must have finished reading the staging tile
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+            }
             // 32 accumulator columns per tensor-memory load: half as many load/wait round trips per staging tile
 #pragma unroll
             for (int sub = 0; sub < BOX / 16; sub += 2) {
@@ -214,7 +261,16 @@ __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUt
 #pragma unroll
                     for (int j = 0; j < 16; j++) rh[j] = r[h * 16 + j];
                     float v[16];
-                    epilogue_values<OutT, ACT>(p, rh, row, n0 + c0 + (sub + h) * 16, b, row_ok, v);
+                    uint4 rp[CHUNKS];
+                    if (res_tile) {  // this lane's own row: the same addresses epilogue_stage overwrites right after
+#pragma unroll
+                        for (int q = 0; q < CHUNKS; q++) {
+                            const int chunk = (sub + h) * CHUNKS + q;
+                            const uint32_t src = stage_base + uint32_t(lane) * 128u + uint32_t((chunk ^ (lane & 7)) * 16);
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rp[q].x), "=r"(rp[q].y), "=r"(rp[q].z), "=r"(rp[q].w) : "r"(src) : "memory");
+                        }
+                    }
+                    epilogue_values<OutT, ACT>(p, rh, row, n0 + c0 + (sub + h) * 16, b, row_ok, v, res_tile, rp);
                     epilogue_stage<OutT>(stage_base, lane, sub + h, v);
                 }
             }
@@ -232,7 +288,8 @@ __device__ __forceinline__ void epilogue_tile(const TcKernelParams& p, const CUt
             tmem_ld_x16(t_addr + uint32_t(c), r);
             tmem_ld_wait();
             float v[16];
-            epilogue_values<OutT, ACT>(p, r, row, n0 + c, b, row_ok, v);
+            const uint4 none[16 / (16 / int(sizeof(OutT)))] = {};
+            epilogue_values<OutT, ACT>(p, r, row, n0 + c, b, row_ok, v, false, none);
             if (row_ok) epilogue_store_direct<OutT>(p, v, row, n0 + c, b);
         }
     }
@@ -302,6 +359,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // everything before this point touches no global memory: under programmatic stream serialization it overlaps
+    // the tail of the kernel launched before this one
+    griddep_wait();
+    griddep_launch_dependents();
 
     const int total_tiles = p.tiles_m * p.tiles_n * p.batch;
     const uint32_t stage_tx = p.a_bytes + uint32_t(p.bn) * 128u;
@@ -523,6 +584,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     cluster_sync();  // the peer's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // everything before this point touches no global memory: under programmatic stream serialization it overlaps
+    // the tail of the kernel launched before this one
+    griddep_wait();
+    griddep_launch_dependents();
 
     const int total_tiles = p.tiles_m * p.tiles_n * p.batch;
 
@@ -677,6 +742,8 @@ __device__ __forceinline__ void split1(float x, __nv_bfloat16& hi, __nv_bfloat16
 __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ X, int64_t rows, int64_t cols, int64_t ld,
                                                          int64_t bs, __nv_bfloat16* __restrict__ hi,
                                                          __nv_bfloat16* __restrict__ lo, int64_t ldo, int64_t obs, int vec) {
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
     const int64_t b = blockIdx.z;
     X += b * bs;
     hi += b * obs;
@@ -708,6 +775,8 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict
 __global__ void __launch_bounds__(256) split_transpose_kernel(const float* __restrict__ X, int64_t rows, int64_t cols,
                                                               int64_t ld, int64_t bs, __nv_bfloat16* __restrict__ hi,
                                                               __nv_bfloat16* __restrict__ lo, int64_t ldo, int64_t obs) {
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
     __shared__ float tile[32][33];
     const int64_t b = blockIdx.z;
     X += b * bs;
@@ -804,13 +873,13 @@ int split_f32_to_bf16x2(Ctx* ctx, const float* X, int64_t rows, int64_t cols, in
         int64_t blocks = ceil_div(items, 256);
         if (blocks > cap) blocks = cap;
         dim3 grid(unsigned(blocks), 1, unsigned(batch));
-        split_rows_kernel<<<grid, 256, 0, ctx->stream>>>(X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride, vec);
+        DOCC_CUDA_TRY(launch_pdl(split_rows_kernel, grid, dim3(256), 0, ctx->stream, X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride, vec));
         return after_launch(ctx, "split_rows_kernel");
     }
     int64_t blocks = ceil_div(rows, 32) * ceil_div(cols, 32);
     if (blocks > cap) blocks = cap;
     dim3 grid(unsigned(blocks), 1, unsigned(batch));
-    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride);
+    DOCC_CUDA_TRY(launch_pdl(split_transpose_kernel, grid, dim3(256), 0, ctx->stream, X, rows, cols, ld, batch_stride, hi, lo, ld_out, out_batch_stride));
     return after_launch(ctx, "split_transpose_kernel");
 }
 
@@ -973,13 +1042,15 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
         cfg.blockDim = dim3(kThreads, 1, 1);
         cfg.dynamicSmemBytes = smem2;
         cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel waits (griddepcontrol.wait) after its set-up
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = 2;
         DOCC_CUDA_TRY(cudaLaunchKernelEx(&cfg, tc_gemm_pair_kernel, maps[0], maps[1], maps[2], maps[3], maps[4], p));
         return after_launch(ctx, "tc_gemm_pair_kernel");
     }
@@ -991,7 +1062,7 @@ int tc_gemm(Ctx* ctx, int ab_format, int64_t M, int64_t N, int64_t K, int64_t ba
     }
     const int64_t total_tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
     const int grid = int(total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count);
-    tc_gemm_kernel<<<grid, kThreads, smem, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    DOCC_CUDA_TRY(launch_pdl(tc_gemm_kernel, dim3(unsigned(grid)), dim3(kThreads), smem, ctx->stream, maps[0], maps[1], maps[2], maps[3], maps[4], p));
     return after_launch(ctx, "tc_gemm_kernel");
 }
 
