@@ -8,9 +8,10 @@
 Prints ONE JSON line. The headline workload (default) is BASELINE config 2: row softmax over a
 fp32 [8192, 4096] tensor, reported as algorithmic HBM GB/s (one read + one write of the tensor).
 A "step" is one pass of the node over one batch of synthetic input. With --gpus N every rank
-processes its own batch (weak scaling over independent units, no data-path collective). ``--strong``
-instead splits ONE conv / attention / encoder-block configuration across the ranks and ends each step
-with one NCCL all-gather of the output shards.
+processes its own batch (weak scaling over independent units, no data-path collective); for the sharded
+configurations (conv, attention, encoder block) the line's extras also carry the split-and-gather reading:
+ONE configuration split across the ranks, each step ending with the in-place NCCL all-gather of the output
+shards (``--strong`` makes that the headline of a single ``--workload``).
 
 ``--impl reference`` times the CPU restatement of the reference's own expansion of the node
 (oracle/, OpenMP over the outermost map as docc's openmp target schedules it) on the host cores.
@@ -30,20 +31,36 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from docc_b200.sharding import gather_shards, shard  # noqa: E402
+from docc_b200.sharding import GatherPlan  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from the ncu captures
-# summarised under profiles/ (softmax_rows_fp32_8192x4096.md, tc_gemm_pair_bf16_8192.md, conv_halo_bf16_config3.md,
-# attention_tc2_bf16_config4.md)
+# (isolated launches: part of the write-back is still in L2 when the kernel ends, which is why the softmax figure is
+# below its 268 MB of algorithmic bytes)
 NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5e6, "attention": 244.6e6}
 
-# Sharded workloads (conv, attention, encoder block): by default every GPU runs the whole configuration on its own
-# data and nothing is exchanged (weak scaling over independent units). --strong splits ONE configuration across the
-# GPUs and ends each step with the NCCL all-gather of the output shards.
+# Sharded workloads (conv, attention, encoder block) at N > 1 GPUs are read two ways. Weak (the headline `value`): every
+# GPU runs the whole configuration on its own data and nothing is exchanged. Split-and-gather (`--strong`, and the
+# `split_gather` list of the line at N > 1): ONE configuration is split over the GPUs and every step ends with the NCCL
+# all-gather of the output shards, in place and chunked so that it overlaps the kernels of the next chunk.
 STRONG = False
+GATHER_CHUNKS = 2
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+# cuBLAS DGEMM 8192^3 through torch on this pool's B200, measured by the builder: tcgen05 has no fp64 kind, so this is
+# the practical ceiling config 1 is held against (not in MEASURED_PEAKS.json)
+FP64_TFLOPS_BUILDER_MEASURED = 35.5
+
+WORKLOAD_TEXT = {
+    "softmax": "softmax fp32 [8192,4096] axis=-1 (BASELINE config 2)",
+    "gemm_f64": "GEMM fp64 1000x1000x1000 (BASELINE config 1)",
+}
+
+
+def headline_config():
+    """The `config` object of the headline line; both arms print exactly this."""
+    return {"workload": WORKLOAD_TEXT["softmax"], "rows_per_gpu": 8192, "cols": 4096,
+            "l2": "inputs larger than L2 and rotated over 4 buffer pairs"}
 
 
 def measured_peaks():
@@ -113,7 +130,7 @@ class ClockSampler:
 # workloads: each returns a dict with a `step()` closure over device-resident inputs, the algorithmic
 # work per step and the roofline that bounds it
 # ------------------------------------------------------------------------------------------------------
-def make_workload(name, torch, ops, rank, world):
+def make_workload(name, torch, ops, rank, world, strong=False):
     dev = torch.device("cuda", torch.cuda.current_device())
     peaks = measured_peaks()
     g = torch.Generator(device="cpu")
@@ -136,8 +153,7 @@ def make_workload(name, torch, ops, rank, world):
         units = 2 * rows * cols * 4  # bytes: one read + one write
         return dict(step=step, units=units, unit="GB/s", scale=1e-9, metric="softmax_hbm_gbs", dtype="f32",
                     bound="hbm", peak=peaks["hbm_gbs"], launches_per_step=1,
-                    config={"workload": "softmax fp32 [8192,4096] axis=-1 (BASELINE config 2)", "rows_per_gpu": rows,
-                            "cols": cols, "l2": "inputs larger than L2 and rotated over 4 buffer pairs"},
+                    config=headline_config(),
                     host_inputs=lambda: [(3 * torch.randn(rows, cols, generator=g))], kind="softmax",
                     h2d=rows * cols * 4, d2h=rows * cols * 4)
 
@@ -151,8 +167,9 @@ def make_workload(name, torch, ops, rank, world):
             ops.gemm(a, b, c)
 
         return dict(step=step, units=2 * 1000 ** 3, unit="TFLOP/s", scale=1e-12, metric="gemm_fp64_tflops", dtype="f64",
-                    bound="tensor", peak=None, launches_per_step=1,
-                    config={"workload": "GEMM fp64 1000x1000x1000 (BASELINE config 1)", "l2": "flushed between steps"},
+                    bound="tensor", peak=FP64_TFLOPS_BUILDER_MEASURED, peak_source="of the builder-measured cuBLAS DGEMM 8192^3 rate",
+                    launches_per_step=1,
+                    config={"workload": WORKLOAD_TEXT["gemm_f64"], "l2": "flushed between steps"},
                     flush=True, kind="gemm", replicas_only=True)
 
     if name in ("gemm_bf16", "gemm_f32"):
@@ -173,23 +190,39 @@ def make_workload(name, torch, ops, rank, world):
                     config={"workload": f"GEMM {name[5:]} 8192^3, B as [N,K]", "l2": "operands (128-256 MB each) larger than L2"},
                     kind="gemm", replicas_only=True)
 
+    # ---- sharded workloads -----------------------------------------------------------------------------
+    # `strong`: ONE configuration is split over the ranks by a GatherPlan (chunk-major, rank order inside a chunk); the
+    # rank's kernels write straight into its slices of the preallocated gathered buffer and the chunks' all-gathers
+    # run in place on a second stream. Otherwise every rank runs the whole configuration on its own (rank-seeded) data.
+    def plan_for(total):
+        if not strong or world == 1:
+            return None
+        chunks = GATHER_CHUNKS if total % (world * GATHER_CHUNKS) == 0 else 1
+        return GatherPlan(total, rank, world, chunks)
+
     if name in ("conv_f32", "conv_bf16"):
         n_total = 32
-        g.manual_seed(2 if STRONG else 2 + 1000 * rank)
+        g.manual_seed(2 if strong else 2 + 1000 * rank)
         x = torch.randn(n_total, 64, 56, 56, generator=g)
-        if STRONG:
-            x = shard(x, rank, world)
+        plan = plan_for(n_total)
+        if plan:
+            x = plan.local_input(x)
         n_local = x.shape[0]
         w = torch.nn.init.kaiming_normal_(torch.empty(128, 64, 3, 3), generator=g)
         bias = torch.zeros(128)
         if name == "conv_bf16":
             x, w = x.bfloat16(), w.bfloat16()
         x, w, bias = x.to(dev), w.to(dev), bias.to(dev)
-        y = torch.empty(n_local, 128, 56, 56, dtype=torch.float32, device=dev)
+        y = torch.empty(n_total if plan else n_local, 128, 56, 56, dtype=torch.float32, device=dev)
+
+        def conv_call(xv, yv):  # the C-ABI call a generated host function makes; output buffer owned by the caller
+            ops.call("docc_b200_conv", ops._prec(xv), ord("s"), 2, ops._arr(xv.shape), ops._arr((3, 3)), ops._arr((1, 1)),
+                     ops._arr((1, 1, 1, 1)), ops._arr((1, 1)), 128, 1, ops._ptr(xv), ops._ptr(w), ops._ptr(bias), ops._ptr(yv), 0)
+
         cargs = (ops._prec(x), ord("s"), 2, ops._arr(x.shape), ops._arr((3, 3)), ops._arr((1, 1)), ops._arr((1, 1, 1, 1)),
                  ops._arr((1, 1)), 128, 1, ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops._ptr(y), 0)
 
-        def step():  # the C-ABI call a generated host function makes; output buffer owned by the caller
+        def step():
             ops.call("docc_b200_conv", *cargs)
             return y
 
@@ -199,20 +232,26 @@ def make_workload(name, torch, ops, rank, world):
                     peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None,
                     config={"workload": f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)",
                             "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv",
-                    gather=n_total if STRONG else None)
+                    plan=plan, full_out=y, gather_bytes=y.numel() * 4,
+                    chunk=(lambda c, out: conv_call(plan.local_chunk(x, c), out)) if plan else None)
 
     if name in ("attention", "attention_causal"):
         causal = name.endswith("causal")
         bh_total = 8
-        g.manual_seed(3 if STRONG else 3 + 1000 * rank)
+        g.manual_seed(3 if strong else 3 + 1000 * rank)
         q, k, v = (torch.randn(bh_total, 16, 2048, 128, generator=g) for _ in range(3))
-        if STRONG:
-            q, k, v = (shard(t_, rank, world) for t_ in (q, k, v))
+        plan = plan_for(bh_total)
+        if plan:
+            q, k, v = (plan.local_input(t_) for t_ in (q, k, v))
         q, k, v = (t_.bfloat16().to(dev) for t_ in (q, k, v))
         b_local = q.shape[0]
-
-        o = torch.empty_like(q)
+        o = torch.empty((bh_total if plan else b_local, 16, 2048, 128), dtype=torch.bfloat16, device=dev)
         null = ops.ctypes.cast(None, ops.ctypes.POINTER(ops.ctypes.c_int64))
+
+        def attn_call(qv, kv, vv, ov):
+            ops.call("docc_b200_attention", ord("b"), qv.shape[0], 16, 2048, 2048, 128, 1.0 / 128 ** 0.5, int(causal), ops._ptr(qv), null,
+                     ops._ptr(kv), null, ops._ptr(vv), null, ops._ptr(ov), null, 0)
+
         aargs = (ord("b"), b_local, 16, 2048, 2048, 128, 1.0 / 128 ** 0.5, int(causal), ops._ptr(q), null, ops._ptr(k), null,
                  ops._ptr(v), null, ops._ptr(o), null, 0)
 
@@ -225,28 +264,41 @@ def make_workload(name, torch, ops, rank, world):
                     bound="tensor", peak=peaks["bf16_tflops"], launches_per_step=1,
                     config={"workload": f"attention bf16 [8,16,2048,128] causal={causal} (BASELINE config 4)",
                             "batch_per_gpu": b_local, "l2": "flushed between steps"}, flush=True, kind="attention",
-                    gather=bh_total if STRONG else None)
+                    plan=plan, full_out=o, gather_bytes=o.numel() * 2,
+                    chunk=(lambda c, out: attn_call(plan.local_chunk(q, c), plan.local_chunk(k, c), plan.local_chunk(v, c), out))
+                    if plan else None)
 
     if name in ("block_f32", "block_bf16"):
         bf = name.endswith("bf16")
         b_total = 32
         d, heads, dff, seq = 1024, 16, 4096, 512
-        torch.manual_seed(4 if STRONG else 4 + 1000 * rank)
+        torch.manual_seed(4 if strong else 4 + 1000 * rank)
         p = {"ln1_g": torch.ones(d), "ln1_b": torch.zeros(d), "ln2_g": torch.ones(d), "ln2_b": torch.zeros(d)}
         for nm, shp in (("w_qkv", (3 * d, d)), ("w_o", (d, d)), ("w_1", (dff, d)), ("w_2", (d, dff))):
             p[nm] = torch.nn.init.xavier_uniform_(torch.empty(*shp))
         for nm, n in (("b_qkv", 3 * d), ("b_o", d), ("b_1", dff), ("b_2", d)):
             p[nm] = torch.zeros(n)
         x = torch.randn(b_total, seq, d)
-        if STRONG:
-            x = shard(x, rank, world)
+        plan = plan_for(b_total)
+        if plan:
+            x = plan.local_input(x)
         b_local = x.shape[0]
         small = ("ln1_g", "ln1_b", "ln2_g", "ln2_b", "b_qkv", "b_o", "b_1", "b_2")
         pd = {k_: (v_.to(dev) if (k_ in small or not bf) else v_.bfloat16().to(dev)) for k_, v_ in p.items()}
         x = (x.bfloat16() if bf else x).to(dev)
+        y = torch.empty((b_total if plan else b_local, seq, d), dtype=x.dtype, device=dev)
+        bp = ops.BlockParams()
+        bp.seq, bp.d_model, bp.n_heads, bp.d_ff, bp.eps = seq, d, heads, dff, 1e-5
+        for f_ in ops.BLOCK_FIELDS:
+            setattr(bp, f_, ops._ptr(pd[f_]).value or 0)
+
+        def block_call(xv, yv):
+            bp.batch = xv.shape[0]
+            ops.call("docc_b200_transformer_block", ops._prec(xv), ops.ctypes.byref(bp), ops._ptr(xv), ops._ptr(yv), 0)
 
         def step():
-            return ops.transformer_block(x, pd, heads)
+            block_call(x, y)
+            return y
 
         T = b_local * seq
         flops = 2 * T * d * (3 * d + d + 2 * dff) + 4 * b_local * heads * seq * seq * (d // heads)
@@ -255,19 +307,30 @@ def make_workload(name, torch, ops, rank, world):
                     peak=peaks["bf16_tflops_sustained"] / (1 if bf else 3), launches_per_step=None,
                     config={"workload": f"pre-LN encoder block {'bf16' if bf else 'fp32'} d1024 h16 ff4096 [32,512,1024] "
                                         "(BASELINE config 5)", "batch_per_gpu": b_local, "l2": "flushed between steps"},
-                    flush=True, kind="block", gather=b_total if STRONG else None)
+                    flush=True, kind="block", plan=plan, full_out=y, gather_bytes=y.numel() * y.element_size(),
+                    chunk=(lambda c, out: block_call(plan.local_chunk(x, c), out)) if plan else None)
 
     raise SystemExit(f"unknown workload {name}")
 
 
 def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clocks=False):
-    """Device-timed loop: W warm-ups, then K steps bracketed by barrier + synchronize, max over ranks."""
+    """Device-timed loop: W warm-ups, then K steps bracketed by barrier + synchronize, max over ranks.
+    Returns (ms per step, launches, clocks, compute ms per step): the last is the time to the end of the step's last
+    kernel when the step ends with a gather (split-and-gather mode), else None."""
     dev_index = torch.cuda.current_device()
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if wl.get("flush") else None
+    plan = wl.get("plan")
+    comm = torch.cuda.Stream() if plan else None
+    main = torch.cuda.current_stream()
+
     def one_step():
-        out = wl["step"]()
-        if world > 1 and wl.get("gather") and out is not None:
-            gather_shards(out, wl["gather"])  # the one collective: NCCL all-gather of the output shards
+        if plan is None:
+            wl["step"]()
+            return None
+        # kernels of chunk c on the main stream, its in-place all-gather on the second stream behind an event
+        events = plan.run(wl["full_out"], wl["chunk"], comm_stream=comm)
+        main.wait_stream(comm)  # the step ends when the gathered buffer is complete
+        return events[-1] if events else None
 
     for _ in range(max(warmup, 3)):
         one_step()
@@ -281,6 +344,7 @@ def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clock
         dist.barrier()
     torch.cuda.synchronize()
     total_ms = 0.0
+    compute_ms = None
     if flush_buf is None:
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -291,14 +355,25 @@ def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clock
         total_ms = start.elapsed_time(end)
     else:
         # L2 flush between steps: time each step with its own event pair so the flush is not counted
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        for s, e in evs:
+        evs = []
+        for _ in range(steps):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             flush_buf.fill_(1)
             s.record()
-            one_step()
+            if plan is None:
+                one_step()
+                mid = None
+            else:
+                mid = torch.cuda.Event(enable_timing=True)
+                events = plan.run(wl["full_out"], wl["chunk"], comm_stream=comm)
+                mid.record()  # after the last chunk's kernels on the main stream
+                main.wait_stream(comm)
             e.record()
+            evs.append((s, mid, e))
         torch.cuda.synchronize()
-        total_ms = sum(s.elapsed_time(e) for s, e in evs)
+        total_ms = sum(s.elapsed_time(e) for s, _, e in evs)
+        if plan is not None:
+            compute_ms = sum(s.elapsed_time(m) for s, m, _ in evs) / steps
     launches = ops.launch_count()
     if world > 1:
         dist.barrier()
@@ -306,10 +381,12 @@ def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clock
     clocks = sampler.stop() if sampler else None
     ms = total_ms / steps
     if world > 1:
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor([ms, compute_ms if compute_ms is not None else 0.0], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms, launches, clocks
+        ms = float(t[0].item())
+        if compute_ms is not None:
+            compute_ms = float(t[1].item())
+    return ms, launches, clocks, compute_ms
 
 
 def e2e_softmax(torch, dist, ops, steps, warmup, world):
@@ -342,15 +419,21 @@ def e2e_softmax(torch, dist, ops, steps, warmup, world):
             "path": "docc_b200_softmax(DOCC_B200_FLAG_HOST_PTRS) on pinned host buffers, chunked H2D/kernel/D2H pipeline"}
 
 
+def _all_cores(oracle):
+    # all the host cores this process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    oracle.set_num_threads(n)
+    return n
+
+
 def cpu_softmax_baseline(budget_s=12.0, max_reps=20):
     """Times the oracle (the reference's 7-loop-nest expansion, OpenMP on the outermost maps) on the full config."""
     import oracle
 
-    # all the host cores this process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
-    try:
-        oracle.set_num_threads(len(os.sched_getaffinity(0)))
-    except AttributeError:
-        oracle.set_num_threads(os.cpu_count() or 1)
+    _all_cores(oracle)
     rows, cols = 8192, 4096
     x = (3 * np.random.RandomState(1).randn(rows, cols)).astype(np.float32)
     oracle.softmax(x[:256], [1])
@@ -366,6 +449,108 @@ def cpu_softmax_baseline(budget_s=12.0, max_reps=20):
             "ms_per_step": best * 1e3}
 
 
+def cpu_extra_baseline(name):
+    """CPU baseline of an extra workload on a bounded sample (a few seconds): the oracle's restatement of the node, or, for
+    config 1, the BLAS dgemm the reference itself calls on the CPU (gemm_node.cpp:449-509; numpy's OpenBLAS stands in for
+    the unpinned -lblas). Returned in the workload's unit, scaled from the sample by the work it contains."""
+    import oracle
+    import torch
+
+    cores = _all_cores(oracle)
+
+    def timed(fn, reps=3):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return float(np.median(ts))
+
+    if name == "gemm_f64":
+        rs = np.random.RandomState(0)
+        a, b = rs.rand(1000, 1000), rs.rand(1000, 1000)
+        torch.set_num_threads(cores)
+        t = timed(lambda: a @ b, 10)
+        return {"value": 2e9 / t * 1e-12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"full 1000^3 problem through OpenBLAS dgemm (numpy), median of 10 ({t * 1e3:.2f} ms)"}
+    if name.startswith("conv"):
+        rs = np.random.RandomState(2)
+        x = rs.randn(2, 64, 56, 56).astype(np.float32)
+        w = (rs.randn(128, 64, 3, 3) * (2.0 / 576) ** 0.5).astype(np.float32)
+        t = timed(lambda: oracle.conv(x, w, np.zeros(128, dtype=np.float32), pads=[1, 1, 1, 1]), 2)
+        return {"value": 2 * 2 * 128 * 56 * 56 * 576 / t * 1e-12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"2 of the 32 images, fp32 oracle loop nest ({t * 1e3:.0f} ms)"}
+    if name.startswith("attention"):
+        rs = np.random.RandomState(3)
+        causal = name.endswith("causal")
+        q, k, v = (rs.randn(1, 2, 2048, 128).astype(np.float32) for _ in range(3))
+        t = timed(lambda: oracle.attention(q, k, v, causal=causal), 2)
+        fl = 4 * 2 * 2048 * 2048 * 128 / (2 if causal else 1)
+        return {"value": fl / t * 1e-12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"2 of the 128 (batch, head) problems, fp32 oracle composition ({t * 1e3:.0f} ms)"}
+    if name.startswith("block"):
+        d, dff, heads, seq = 1024, 4096, 16, 512
+        rs = np.random.RandomState(4)
+        p = {"ln1_g": np.ones(d, np.float32), "ln1_b": np.zeros(d, np.float32), "ln2_g": np.ones(d, np.float32), "ln2_b": np.zeros(d, np.float32)}
+        for nm, shp in (("w_qkv", (3 * d, d)), ("w_o", (d, d)), ("w_1", (dff, d)), ("w_2", (d, dff))):
+            p[nm] = (rs.rand(*shp).astype(np.float32) - 0.5) * 2 * (6.0 / sum(shp)) ** 0.5
+        for nm, n in (("b_qkv", 3 * d), ("b_o", d), ("b_1", dff), ("b_2", d)):
+            p[nm] = np.zeros(n, np.float32)
+        x = rs.randn(1, seq, d).astype(np.float32)
+        t = timed(lambda: oracle.transformer_block(x, p, heads), 2)
+        fl = 2 * seq * d * (3 * d + d + 2 * dff) + 4 * heads * seq * seq * (d // heads)
+        return {"value": fl / t * 1e-12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"1 of the 32 sequences, fp32 oracle composition ({t * 1e3:.0f} ms)"}
+    return None
+
+
+def e2e_extra(name, torch, ops, steps=5):
+    """The workload through the C ABI with HOST buffers (pinned): H2D of the inputs, the kernels and D2H of the result are
+    inside the timed region, as generated host code with the "WithTransfers" dispatchers does it."""
+    pin = lambda t_: t_.contiguous().pin_memory()
+    if name == "gemm_f64":
+        rs = np.random.RandomState(0)
+        a, b = pin(torch.from_numpy(rs.rand(1000, 1000))), pin(torch.from_numpy(rs.rand(1000, 1000)))
+        c = pin(torch.empty(1000, 1000, dtype=torch.float64))
+        one, zero = ops.ctypes.c_double(1.0), ops.ctypes.c_double(0.0)
+        vp = ops.ctypes.c_void_p
+
+        def call():
+            ops.call("docc_b200_gemm", ord("d"), 101, 111, 111, 1000, 1000, 1000, ops.ctypes.cast(ops.ctypes.pointer(one), vp), vp(a.data_ptr()), 1000,
+                     vp(b.data_ptr()), 1000, ops.ctypes.cast(ops.ctypes.pointer(zero), vp), vp(c.data_ptr()), 1000, ops.FLAG_HOST_PTRS)
+
+        units, h2d, d2h = 2e9, 16e6, 8e6
+    elif name in ("conv_f32", "conv_bf16"):
+        g = torch.Generator().manual_seed(2)
+        x = torch.randn(32, 64, 56, 56, generator=g)
+        w = torch.nn.init.kaiming_normal_(torch.empty(128, 64, 3, 3), generator=g)
+        if name == "conv_bf16":
+            x, w = x.bfloat16(), w.bfloat16()
+        x, w, bias = pin(x), pin(w), pin(torch.zeros(128))
+        y = pin(torch.empty(32, 128, 56, 56))
+        vp = ops.ctypes.c_void_p
+
+        def call():
+            ops.call("docc_b200_conv", ops._prec(x), ord("s"), 2, ops._arr(x.shape), ops._arr((3, 3)), ops._arr((1, 1)), ops._arr((1, 1, 1, 1)),
+                     ops._arr((1, 1)), 128, 1, vp(x.data_ptr()), vp(w.data_ptr()), vp(bias.data_ptr()), vp(y.data_ptr()), ops.FLAG_HOST_PTRS)
+
+        units = 2 * 32 * 128 * 56 * 56 * 576
+        h2d, d2h = x.numel() * x.element_size() + w.numel() * w.element_size() + 512, y.numel() * 4
+    else:
+        return None
+    for _ in range(2):
+        call()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        call()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    return {"value": units / (ms * 1e-3) * 1e-12, "unit": "TFLOP/s", "ms_per_step": ms, "h2d_bytes_per_step": int(h2d),
+            "d2h_bytes_per_step": int(d2h), "path": "C ABI with DOCC_B200_FLAG_HOST_PTRS on pinned host buffers"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -374,7 +559,7 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "softmax_hbm_gbs", "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "softmax fp32 [8192,4096] axis=-1 (BASELINE config 2)"},
+            "config": headline_config(),
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "CPU restatement of docc's SoftmaxNode expansion (7 loop nests, 6 temporaries), OpenMP on the outermost "
@@ -391,7 +576,7 @@ def main():
     ap.add_argument("--workload", default="softmax")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--strong", action="store_true",
-                    help="split one conv / attention / block configuration across the GPUs and all-gather the outputs")
+                    help="headline the split-and-gather reading of a sharded workload (one configuration split over the GPUs)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the e2e and CPU-baseline legs (profiling runs)")
     ap.add_argument("--extra-steps", type=int, default=10)
     args = ap.parse_args()
@@ -418,20 +603,24 @@ def main():
     ops.init(local_rank)
     ops.set_stream(torch.cuda.current_stream().cuda_stream)
 
-    wl = make_workload(args.workload, torch, ops, rank, world)
-    ms, launches, clocks = time_workload(wl, torch, dist, ops, args.steps, args.warmup, world, rank, sample_clocks=True)
+    wl = make_workload(args.workload, torch, ops, rank, world, strong=STRONG)
+    ms, launches, clocks, compute_ms = time_workload(wl, torch, dist, ops, args.steps, args.warmup, world, rank, sample_clocks=True)
     peaks = measured_peaks()
     per_gpu = wl["units"] / (ms * 1e-3) * wl["scale"]
     value = per_gpu * (1 if wl.get("replicas_only") else world)
     roof = {"bound": wl["bound"], "achieved": per_gpu, "peak": wl["peak"], "unit": wl["unit"],
             "frac": (per_gpu / wl["peak"]) if wl["peak"] else None, "traffic": None,
-            "peak_source": f"of {peaks['source']}"}
+            "peak_source": wl.get("peak_source", f"of {peaks['source']}")}
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
 
+    split = bool(wl.get("plan"))
     line = {"metric": wl["metric"], "value": value, "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "replicas" if wl.get("replicas_only") else ("strong" if (STRONG and wl.get("gather")) else "weak"), "vs_baseline": None, "dtype": wl["dtype"],
+            "scaling": "replicas" if wl.get("replicas_only") else ("strong" if split else "weak"), "vs_baseline": None, "dtype": wl["dtype"],
             "data": "synthetic", "config": wl["config"], "roofline": roof, "gpu_launches": int(launches), "clocks": clocks}
+    if split:
+        line["compute_ms"] = compute_ms
+        line["gather_exposed_ms"] = ms - compute_ms if compute_ms is not None else None
 
     if args.workload == "softmax" and not args.kernel_only:
         line["e2e"] = e2e_softmax(torch, dist, ops, max(args.steps // 5, 5), args.warmup, world)
@@ -444,17 +633,38 @@ def main():
         for nm in names:
             try:
                 w2 = make_workload(nm, torch, ops, rank, world)
-                if w2.get("replicas_only") and world > 1 and rank != 0:
-                    pass
-                ms2, l2, _ = time_workload(w2, torch, dist, ops, args.extra_steps, 3, world, rank)
+                ms2, l2, clk2, _ = time_workload(w2, torch, dist, ops, args.extra_steps, 3, world, rank, sample_clocks=(rank == 0))
                 pg = w2["units"] / (ms2 * 1e-3) * w2["scale"]
-                extras.append({"metric": w2["metric"], "value": pg * (1 if w2.get("replicas_only") else world),
-                               "unit": w2["unit"], "ms_per_step": ms2, "dtype": w2["dtype"], "config": w2["config"],
-                               "roofline": {"bound": w2["bound"], "achieved": pg, "peak": w2["peak"],
-                                            "frac": (pg / w2["peak"]) if w2["peak"] else None},
-                               "gpu_launches": int(l2)})
+                ex = {"metric": w2["metric"], "value": pg * (1 if w2.get("replicas_only") else world),
+                      "unit": w2["unit"], "ms_per_step": ms2, "dtype": w2["dtype"], "config": w2["config"],
+                      "roofline": {"bound": w2["bound"], "achieved": pg, "peak": w2["peak"],
+                                   "frac": (pg / w2["peak"]) if w2["peak"] else None,
+                                   "peak_source": w2.get("peak_source", f"of {peaks['source']}")},
+                      "gpu_launches": int(l2), "clocks": clk2}
                 del w2
                 torch.cuda.empty_cache()
+                if world == 1 and not args.kernel_only:
+                    e2e = e2e_extra(nm, torch, ops)
+                    if e2e:
+                        ex["e2e"] = e2e
+                    cb = cpu_extra_baseline(nm)
+                    if cb:
+                        ex["cpu_baseline"] = cb
+                # the split-and-gather reading of the sharded configurations, next to the weak one
+                if world > 1 and nm not in ("gemm_f64", "gemm_bf16", "gemm_f32"):
+                    w3 = make_workload(nm, torch, ops, rank, world, strong=True)
+                    ms3, _, _, comp3 = time_workload(w3, torch, dist, ops, args.extra_steps, 3, world, rank)
+                    ex["split_gather"] = {
+                        "ms_per_step": ms3, "compute_ms": comp3, "gather_exposed_ms": ms3 - comp3 if comp3 is not None else None,
+                        "speedup_vs_one_gpu": ms2 / ms3, "chunks": w3["plan"].chunks,
+                        "gathered_bytes_per_rank": int(w3["gather_bytes"] * (world - 1) // world),
+                        "nvlink_bound_ms": w3["gather_bytes"] * (world - 1) / world / 770e9 * 1e3,
+                        "note": "one configuration split over the GPUs; in-place NCCL all-gather per chunk on a second stream; "
+                                "speed-up against the same configuration on one GPU of this run (the weak reading above); "
+                                "NVLink bound = bytes a rank receives / 770 GB/s measured peer copy rate"}
+                    del w3
+                    torch.cuda.empty_cache()
+                extras.append(ex)
             except Exception as exc:  # an extra must never take the headline line down
                 extras.append({"metric": nm, "error": f"{type(exc).__name__}: {exc}"[:300]})
         line["extras"] = extras

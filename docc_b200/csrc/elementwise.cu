@@ -5,6 +5,7 @@
 // with 128-bit accesses and every output byte written once.
 #include "common.cuh"
 #include "device_math.cuh"
+#include "ptx.cuh"
 
 namespace docc_b200 {
 namespace {
@@ -107,60 +108,93 @@ __global__ void __launch_bounds__(BLOCK) layernorm_kernel(const T* __restrict__ 
     }
 }
 
-// Rows that fit one warp's registers, many rows per warp: every warp walks rows w, w + W, w + 2W, ... (W = warps in the
-// grid) with its slice of gamma / beta held in registers for the whole walk and the next row's loads issued before the
-// current row is reduced, so that loads are in flight all the time. Against one row group per block this removes the
-// per-row parameter loads (16 of the 24 memory instructions a thread issued per bf16 row of 1024) and the
-// load -> reduce -> store -> exit bubbles of short-lived blocks.
+// Rows that fit one warp's registers, many rows per warp, rows staged through shared memory by bulk copies.
+// A warp-per-row LayerNorm holds a row in registers, so the bytes a warp can have in flight are bounded by its
+// registers: with a 1024-wide bf16 row that was 2 KB per warp, 32 KB per SM, too little to cover HBM latency
+// (measured 3.4 TB/s). Here every warp owns a ring of kLnStages row buffers in shared memory that one lane keeps
+// filled with cp.async.bulk copies (completion on an mbarrier per slot): 3 rows per warp and 16 warps per SM are in
+// flight whatever the register count. The warp walks rows w, w + W, w + 2W, ... (W = warps in the grid), reads its row
+// and the gamma / beta slice from shared memory, and stores the result straight from registers (coalesced 16-byte
+// stores). gamma / beta are staged once per block.
+constexpr int kLnStages = 3;
+constexpr int kLnWarps = 16;
+
 template <typename T, int VPT>
-__global__ void __launch_bounds__(256, 2) layernorm_warp_rows_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
-                                                                     const float* __restrict__ beta, float eps, T* __restrict__ Y,
-                                                                     int64_t rows, int64_t cols) {
-    griddep_wait_all();
+__global__ void __launch_bounds__(kLnWarps * 32, 1) layernorm_bulk_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
+                                                                         const float* __restrict__ beta, float eps, T* __restrict__ Y,
+                                                                         int64_t rows, int64_t cols) {
     constexpr int VEC = 16 / sizeof(T);
     using P = Pack<T, VEC>;
-    const int lane = threadIdx.x & 31;
+    extern __shared__ __align__(128) uint8_t ln_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t row_bytes = uint32_t(cols) * uint32_t(sizeof(T));
+    const uint32_t row_pitch = (row_bytes + 127u) & ~127u;
+    // layout: gamma [cols] fp32, beta [cols] fp32, mbarriers [warps][stages], row buffers [warps][stages][row_pitch]
+    float* s_gamma = reinterpret_cast<float*>(ln_smem);
+    float* s_beta = s_gamma + cols;
+    const uint32_t bars = ptx::smem_u32(ln_smem) + ((uint32_t(cols) * 8u + 127u) & ~127u);
+    const uint32_t bufs = bars + ((uint32_t(kLnWarps * kLnStages) * 8u + 127u) & ~127u);
+    const uint32_t my_bar = bars + uint32_t(warp * kLnStages) * 8u;
+    const uint32_t my_buf = bufs + uint32_t(warp * kLnStages) * row_pitch;
+    if (lane == 0) {
+        for (int s = 0; s < kLnStages; s++) ptx::mbar_init(my_bar + 8u * s, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncwarp();
+    griddep_wait_all();  // nothing above touches global memory
     const int64_t packs = cols / VEC;
-    const int64_t warps = int64_t(gridDim.x) * 8;
-    int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    float gm[VPT][VEC], bt[VPT][VEC];
-#pragma unroll
-    for (int i = 0; i < VPT; i++) {
-        const int64_t p = int64_t(i) * 32 + lane;
-#pragma unroll
-        for (int q4 = 0; q4 < VEC / 4; q4++) {
-            const bool in = p < packs;
-            const float4 g4 = (gamma && in) ? __ldg(reinterpret_cast<const float4*>(gamma + p * VEC) + q4) : make_float4(1.f, 1.f, 1.f, 1.f);
-            const float4 b4 = (beta && in) ? __ldg(reinterpret_cast<const float4*>(beta + p * VEC) + q4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            gm[i][q4 * 4 + 0] = g4.x; gm[i][q4 * 4 + 1] = g4.y; gm[i][q4 * 4 + 2] = g4.z; gm[i][q4 * 4 + 3] = g4.w;
-            bt[i][q4 * 4 + 0] = b4.x; bt[i][q4 * 4 + 1] = b4.y; bt[i][q4 * 4 + 2] = b4.z; bt[i][q4 * 4 + 3] = b4.w;
+    const int64_t warps = int64_t(gridDim.x) * kLnWarps;
+    const int64_t first = int64_t(blockIdx.x) * kLnWarps + warp;
+    // fill this warp's ring, then stage the parameters while those copies fly
+    if (lane == 0) {
+        for (int s = 0; s < kLnStages; s++) {
+            const int64_t r = first + int64_t(s) * warps;
+            if (r < rows) {
+                ptx::mbar_arrive_expect_tx(my_bar + 8u * s, row_bytes);
+                ptx::bulk_load_1d(my_buf + uint32_t(s) * row_pitch, X + r * cols, row_bytes, my_bar + 8u * s);
+            }
         }
     }
-    P nxt[VPT];
-    auto load_row = [&](int64_t r) {
-        const P* xr = reinterpret_cast<const P*>(X + r * cols);
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        s_gamma[c] = gamma ? gamma[c] : 1.f;
+        s_beta[c] = beta ? beta[c] : 0.f;
+    }
+    __syncthreads();
+    const float inv_cols = 1.f / float(cols);
+    uint32_t stage = 0, phase = 0;
+    for (int64_t row = first; row < rows; row += warps) {
+        if (!ptx::mbar_wait(my_bar + 8u * stage, phase)) return;  // bounded; a copy that never lands ends the warp
+        P cur[VPT];
+        const uint32_t src = my_buf + stage * row_pitch;
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
             const int64_t p = int64_t(i) * 32 + lane;
-            if (p < packs) nxt[i] = load_pack(xr + p);
+            if (p < packs) {
+                uint4 w;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(src + uint32_t(p) * 16u) : "memory");
+                cur[i] = *reinterpret_cast<const P*>(&w);
+            }
         }
-    };
-    load_row(row);
-    const float inv_cols = 1.f / float(cols);
-    for (; row < rows; row += warps) {
-        // the row stays in its storage type (half the registers for 16-bit rows); conversions are repeated per pass
-        P cur[VPT];
+        __syncwarp();  // every lane has its part of the row in registers: the slot can be refilled
+        if (lane == 0) {
+            const int64_t r = row + int64_t(kLnStages) * warps;
+            if (r < rows) {
+                ptx::mbar_arrive_expect_tx(my_bar + 8u * stage, row_bytes);
+                ptx::bulk_load_1d(my_buf + stage * row_pitch, X + r * cols, row_bytes, my_bar + 8u * stage);
+            }
+        }
+        if (++stage == uint32_t(kLnStages)) {
+            stage = 0;
+            phase ^= 1u;
+        }
         float s = 0.f;
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
-            cur[i] = nxt[i];
             if (int64_t(i) * 32 + lane < packs) {
 #pragma unroll
                 for (int e = 0; e < VEC; e++) s += to_float(cur[i].v[e]);
             }
         }
-        if (row + warps < rows) load_row(row + warps);  // in flight during the reductions and the stores below
         const float mean = warp_sum_f(s) * inv_cols;
         float q = 0.f;
 #pragma unroll
@@ -181,7 +215,14 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_rows_kernel(const T* __
             if (p < packs) {
                 P pk;
 #pragma unroll
-                for (int e = 0; e < VEC; e++) pk.v[e] = from_float<T>((to_float(cur[i].v[e]) - mean) * rstd * gm[i][e] + bt[i][e]);
+                for (int q4 = 0; q4 < VEC / 4; q4++) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(s_gamma + p * VEC + q4 * 4);
+                    const float4 b4 = *reinterpret_cast<const float4*>(s_beta + p * VEC + q4 * 4);
+                    pk.v[q4 * 4 + 0] = from_float<T>((to_float(cur[i].v[q4 * 4 + 0]) - mean) * rstd * g4.x + b4.x);
+                    pk.v[q4 * 4 + 1] = from_float<T>((to_float(cur[i].v[q4 * 4 + 1]) - mean) * rstd * g4.y + b4.y);
+                    pk.v[q4 * 4 + 2] = from_float<T>((to_float(cur[i].v[q4 * 4 + 2]) - mean) * rstd * g4.z + b4.z);
+                    pk.v[q4 * 4 + 3] = from_float<T>((to_float(cur[i].v[q4 * 4 + 3]) - mean) * rstd * g4.w + b4.w);
+                }
                 store_pack(yr + p, pk);
             }
         }
@@ -212,12 +253,20 @@ __global__ void __launch_bounds__(256) layernorm_generic_kernel(const T* __restr
 }
 
 template <typename T, int VPT>
-int launch_ln_warp_rows(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
-    // two resident blocks of eight warps per SM; fewer when there are not that many rows
-    int64_t blocks = ceil_div(rows, 8);
-    if (blocks > int64_t(ctx->sm_count) * 2) blocks = int64_t(ctx->sm_count) * 2;
-    DOCC_CUDA_TRY(launch_pdl(layernorm_warp_rows_kernel<T, VPT>, dim3(unsigned(blocks)), dim3(256), 0, ctx->stream, X, g, b, eps, Y, rows, cols));
-    return after_launch(ctx, "layernorm_warp_rows_kernel");
+int launch_ln_bulk(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
+    static bool attr_done[16] = {};  // per instantiation and device
+    const size_t row_pitch = (size_t(cols) * sizeof(T) + 127) & ~size_t(127);
+    const size_t smem = ((size_t(cols) * 8 + 127) & ~size_t(127)) + ((size_t(kLnWarps * kLnStages) * 8 + 127) & ~size_t(127)) +
+                        size_t(kLnWarps * kLnStages) * row_pitch;
+    auto kern = layernorm_bulk_kernel<T, VPT>;
+    if (!attr_done[ctx->device & 15]) {
+        DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_done[ctx->device & 15] = true;
+    }
+    int64_t blocks = ceil_div(rows, kLnWarps);
+    if (blocks > ctx->sm_count) blocks = ctx->sm_count;
+    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(blocks)), dim3(kLnWarps * 32), smem, ctx->stream, X, g, b, eps, Y, rows, cols));
+    return after_launch(ctx, "layernorm_bulk_kernel");
 }
 
 template <typename T, int VPT, int TPR>
@@ -242,11 +291,13 @@ int layernorm_device(Ctx* ctx, int64_t rows, int64_t cols, const T* X, const flo
     if (aligned && packs <= 2048) {
         if (packs <= 32) return launch_ln<T, 1, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 64) return launch_ln<T, 2, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
-        if (packs <= 128) {
-            // enough rows for every warp of a resident-size grid to amortise its parameter registers over a few rows
-            if (rows >= int64_t(ctx->sm_count) * 64) return launch_ln_warp_rows<T, 4>(ctx, X, g, b, float(eps), Y, rows, cols);
-            return launch_ln<T, 4, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
-        }
+        // many rows: the persistent kernel that stages rows through shared memory (rows up to 4 KB keep 48 of them per SM
+        // in flight inside the 227 KB budget)
+        const bool many = rows >= int64_t(ctx->sm_count) * kLnWarps * 2 && size_t(cols) * sizeof(T) <= 4096;
+        if (many && packs <= 64) return launch_ln_bulk<T, 2>(ctx, X, g, b, float(eps), Y, rows, cols);
+        if (many && packs <= 128) return launch_ln_bulk<T, 4>(ctx, X, g, b, float(eps), Y, rows, cols);
+        if (many && packs <= 256) return launch_ln_bulk<T, 8>(ctx, X, g, b, float(eps), Y, rows, cols);
+        if (packs <= 128) return launch_ln<T, 4, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 256) return launch_ln<T, 8, 32>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 512) return launch_ln<T, 4, 128>(ctx, X, g, b, float(eps), Y, rows, cols);
         if (packs <= 1024) return launch_ln<T, 8, 128>(ctx, X, g, b, float(eps), Y, rows, cols);
@@ -403,11 +454,14 @@ extern "C" int docc_b200_layernorm(int prec, int64_t rows, int64_t cols, const v
     DOCC_TRY(get_ctx(&ctx));
     DOCC_REQUIRE(rows >= 0 && cols >= 0, "layernorm: negative extent");
     DOCC_REQUIRE(rows * cols == 0 || (X && Y), "layernorm: NULL data pointer");
-    DOCC_REQUIRE(prec == DOCC_B200_PREC_S || prec == DOCC_B200_PREC_B, "layernorm: precision %d not supported (use 's' or 'b')", prec);
+    DOCC_REQUIRE(prec == DOCC_B200_PREC_S || prec == DOCC_B200_PREC_B || prec == DOCC_B200_PREC_H,
+                 "layernorm: precision %d not supported (use 's', 'b' or 'h')", prec);
     const size_t es = prec_size(prec);
     auto run = [&](const void* x, const float* g, const float* b, void* y) {
         if (prec == DOCC_B200_PREC_S)
             return layernorm_device<float>(ctx, rows, cols, static_cast<const float*>(x), g, b, eps, static_cast<float*>(y));
+        if (prec == DOCC_B200_PREC_H)
+            return layernorm_device<__half>(ctx, rows, cols, static_cast<const __half*>(x), g, b, eps, static_cast<__half*>(y));
         return layernorm_device<__nv_bfloat16>(ctx, rows, cols, static_cast<const __nv_bfloat16*>(x), g, b, eps,
                                                static_cast<__nv_bfloat16*>(y));
     };

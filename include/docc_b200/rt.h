@@ -244,7 +244,7 @@ int docc_b200_attention(int prec, int64_t B, int64_t H, int64_t Sq, int64_t Skv,
 /* ---- LayerNorm ---------------------------------------------------------------------
  * Y = (X - mean) / sqrt(var + eps) * gamma + beta over the last dimension, population
  * variance (the MeanNode / StdNode building blocks, mean_node.cpp:77-118,
- * std_node.cpp:147-222). gamma/beta are fp32 and may be NULL. prec 's' or 'b'. */
+ * std_node.cpp:147-222). gamma/beta are fp32 and may be NULL. prec 's', 'b' or 'h'. */
 int docc_b200_layernorm(int prec, int64_t rows, int64_t cols,
                         const void* X, const void* gamma, const void* beta,
                         double eps, void* Y, int flags);

@@ -457,6 +457,25 @@ def test_layernorm(rt, rows, cols):
     assert relerr(ops.layernorm(x), oracle.layernorm(x)) <= TOL_F32
 
 
+# Many rows take the persistent kernel that stages rows through shared memory with bulk copies (a ring per warp):
+# row counts that are not a multiple of the warps in the grid, widths that leave lanes idle, with and without parameters.
+@pytest.mark.parametrize("rows,cols,dtype", [(16384, 1024, torch.bfloat16), (5000, 1024, torch.float32), (4801, 768, torch.bfloat16),
+                                             (6007, 2048, torch.bfloat16), (9000, 520, torch.float32), (4736, 256, torch.float16)])
+def test_layernorm_many_rows(rt, rows, cols, dtype):
+    torch.manual_seed(rows)
+    x = (torch.randn(rows, cols) * 2 + 0.5).to(dtype)
+    g, b = torch.rand(cols) + 0.5, torch.randn(cols)
+    tol = TOL_F32 if dtype == torch.float32 else TOL_16
+    ref = torch.nn.functional.layer_norm(x.double(), (cols,), g.double(), b.double()).numpy()
+    got = host(ops.layernorm(x.cuda(), g.cuda(), b.cuda()))
+    assert relerr(got, ref) <= tol
+    sl = slice(rows - 40, rows)  # the oracle on the last rows (the ones the ring handles in its final, partial round)
+    if dtype != torch.float16:
+        ref_o = oracle.layernorm(x[sl].float().numpy(), g.numpy(), b.numpy())
+        assert relerr(got[sl], ref_o) <= tol
+    assert relerr(host(ops.layernorm(x.cuda())), torch.nn.functional.layer_norm(x.double(), (cols,)).numpy()) <= tol
+
+
 def test_layernorm_bf16(rt):
     torch.manual_seed(6)
     x = torch.randn(32, 1024).bfloat16()
