@@ -43,7 +43,11 @@ NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5
 # `split_gather` list of the line at N > 1): ONE configuration is split over the GPUs and every step ends with the NCCL
 # all-gather of the output shards, in place and chunked so that it overlaps the kernels of the next chunk.
 STRONG = False
-GATHER_CHUNKS = 2
+# Chunks per step of the split-and-gather mode. More than one overlaps the gather of a chunk with the kernels of the next,
+# but at these sizes it costs more than it hides: half-size calls fill the 148 SMs worse (attention: 256 work items per
+# call are 1.7 waves) and every extra launch is paid on the host. Measured at 2 GPUs, encoder block bf16: 0.43 ms with
+# two chunks against 0.29 ms with one.
+GATHER_CHUNKS = 1
 
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -124,6 +128,36 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def bind_near_gpu(device_index):
+    """Restricts this process to the CPU cores of the NUMA node its GPU hangs off (read from sysfs), so that pinned host
+    buffers are first touched, and the copy threads run, next to the GPU's PCIe root. With eight ranks on a two-socket
+    host the end-to-end path (H2D + kernel + D2H through pinned memory) is bounded by host memory traffic; unbound ranks
+    all land on one socket. Best effort: returns a description, never raises."""
+    info = {"bound": False}
+    try:
+        out = subprocess.run(["nvidia-smi", f"--id={device_index}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=10).stdout.strip()
+        bus = out.lower()
+        if bus.startswith("00000000:"):
+            bus = bus[4:]  # sysfs uses a 4-digit domain
+        node_path = f"/sys/bus/pci/devices/{bus}/numa_node"
+        node = int(open(node_path).read().strip())
+        info["pci"], info["numa_node"] = bus, node
+        if node < 0:
+            return info
+        cpus = []
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.extend(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["bound"], info["cpus"] = True, len(allowed)
+    except Exception as exc:
+        info["error"] = f"{type(exc).__name__}: {exc}"[:120]
+    return info
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -315,71 +349,64 @@ def make_workload(name, torch, ops, rank, world, strong=False):
 
 def time_workload(wl, torch, dist, ops, steps, warmup, world, rank, sample_clocks=False):
     """Device-timed loop: W warm-ups, then K steps bracketed by barrier + synchronize, max over ranks.
-    Returns (ms per step, launches, clocks, compute ms per step): the last is the time to the end of the step's last
-    kernel when the step ends with a gather (split-and-gather mode), else None."""
+    Returns (ms per step, launches, clocks, compute ms per step): the last is the time of the step's kernels alone
+    (same chunks, no gather) when the step ends with a gather (split-and-gather mode), else None."""
     dev_index = torch.cuda.current_device()
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if wl.get("flush") else None
     plan = wl.get("plan")
     comm = torch.cuda.Stream() if plan else None
-    main = torch.cuda.current_stream()
 
-    def one_step():
+    def full_step():
         if plan is None:
             wl["step"]()
-            return None
-        # kernels of chunk c on the main stream, its in-place all-gather on the second stream behind an event
-        events = plan.run(wl["full_out"], wl["chunk"], comm_stream=comm)
-        main.wait_stream(comm)  # the step ends when the gathered buffer is complete
-        return events[-1] if events else None
+            return
+        # kernels of chunk c on the current stream, its in-place all-gather on the second stream behind an event
+        plan.run(wl["full_out"], wl["chunk"], comm_stream=comm)
+        torch.cuda.current_stream().wait_stream(comm)  # the step ends when the gathered buffer is complete
+
+    def compute_only():
+        for c in range(plan.chunks):
+            wl["chunk"](c, plan.out_slice(wl["full_out"], c))
 
     for _ in range(max(warmup, 3)):
-        one_step()
+        full_step()
     torch.cuda.synchronize()
+    one_step, comp_step = full_step, (compute_only if plan else None)
     sampler = ClockSampler(dev_index) if sample_clocks else None
     if sampler:
         sampler.start()
         time.sleep(0.3)
     ops.launch_count(reset=True)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    total_ms = 0.0
-    compute_ms = None
-    if flush_buf is None:
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            one_step()
-        end.record()
+
+    def timed(fn):
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
-        total_ms = start.elapsed_time(end)
-    else:
+        if flush_buf is None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            return start.elapsed_time(end) / steps
         # L2 flush between steps: time each step with its own event pair so the flush is not counted
-        evs = []
-        for _ in range(steps):
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in evs:
             flush_buf.fill_(1)
             s.record()
-            if plan is None:
-                one_step()
-                mid = None
-            else:
-                mid = torch.cuda.Event(enable_timing=True)
-                events = plan.run(wl["full_out"], wl["chunk"], comm_stream=comm)
-                mid.record()  # after the last chunk's kernels on the main stream
-                main.wait_stream(comm)
+            fn()
             e.record()
-            evs.append((s, mid, e))
         torch.cuda.synchronize()
-        total_ms = sum(s.elapsed_time(e) for s, _, e in evs)
-        if plan is not None:
-            compute_ms = sum(s.elapsed_time(m) for s, m, _ in evs) / steps
+        return sum(s.elapsed_time(e) for s, e in evs) / steps
+
+    ms = timed(one_step)
     launches = ops.launch_count()
+    compute_ms = timed(comp_step) if plan is not None else None
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
-    ms = total_ms / steps
     if world > 1:
         t = torch.tensor([ms, compute_ms if compute_ms is not None else 0.0], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -568,6 +595,7 @@ def run_reference(args):
 
 
 def main():
+    global STRONG, GATHER_CHUNKS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -579,13 +607,14 @@ def main():
                     help="headline the split-and-gather reading of a sharded workload (one configuration split over the GPUs)")
     ap.add_argument("--kernel-only", action="store_true", help="skip the e2e and CPU-baseline legs (profiling runs)")
     ap.add_argument("--extra-steps", type=int, default=10)
+    ap.add_argument("--gather-chunks", type=int, default=GATHER_CHUNKS, help="chunks per step in the split-and-gather mode")
     args = ap.parse_args()
 
     if args.impl == "reference":
         run_reference(args)
         return
-    global STRONG
     STRONG = bool(args.strong)
+    GATHER_CHUNKS = max(1, int(args.gather_chunks))
 
     import torch
     import torch.distributed as dist
@@ -598,6 +627,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
+    numa = bind_near_gpu(local_rank) if world > 1 else {"bound": False, "note": "single rank: left unbound"}
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ops.init(local_rank)
@@ -624,6 +654,7 @@ def main():
 
     if args.workload == "softmax" and not args.kernel_only:
         line["e2e"] = e2e_softmax(torch, dist, ops, max(args.steps // 5, 5), args.warmup, world)
+        line["e2e"]["host_binding_rank0"] = numa
         if rank == 0 and world == 1:
             line["cpu_baseline"] = {k: v for k, v in cpu_softmax_baseline().items() if k != "ms_per_step"}
 
@@ -659,7 +690,8 @@ def main():
                         "speedup_vs_one_gpu": ms2 / ms3, "chunks": w3["plan"].chunks,
                         "gathered_bytes_per_rank": int(w3["gather_bytes"] * (world - 1) // world),
                         "nvlink_bound_ms": w3["gather_bytes"] * (world - 1) / world / 770e9 * 1e3,
-                        "note": "one configuration split over the GPUs; in-place NCCL all-gather per chunk on a second stream; "
+                        "note": "one configuration split over the GPUs; in-place NCCL all-gather per chunk on a second stream; compute_ms = "
+                                "the same chunks' kernels alone (launches issued one by one: short steps are paced by the host); "
                                 "speed-up against the same configuration on one GPU of this run (the weak reading above); "
                                 "NVLink bound = bytes a rank receives / 770 GB/s measured peer copy rate"}
                     del w3

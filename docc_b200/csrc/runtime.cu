@@ -357,11 +357,13 @@ int docc_b200_set_stream(void* stream) {
         cudaEvent_t ev = c->switch_event;
         cudaError_t e = cudaEventRecord(ev, c->stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(next, ev, 0);
+        const cudaStream_t old = c->stream;
+        c->stream = next;  // the switch itself always takes effect
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
+            (void)old;
             DOCC_CUDA_TRY(cudaDeviceSynchronize());  // e.g. the old stream handle was destroyed by its owner
         }
-        c->stream = next;
     }
     return DOCC_B200_OK;
 }

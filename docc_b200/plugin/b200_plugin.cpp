@@ -7,6 +7,7 @@
 #include <sdfg/types/utils.h>
 
 #include "b200_emit.h"
+#include "b200_map_dispatcher.h"
 
 namespace docc::target::b200 {
 
@@ -357,6 +358,18 @@ void register_plugin(plugins::Context& context) {
     both(LibraryNodeType_LayerNorm.value(), make_factory<LayerNormNodeDispatcher_B200>(true), make_factory<LayerNormNodeDispatcher_B200>(false));
     // transfers / allocations: the CUDA offloading node (its serializer is registered by the CUDA plugin, plugin.h:47-52)
     reg.register_library_node_dispatcher("CUDAOffloading::" + ImplementationType_B200.value(), make_factory<OffloadingNodeDispatcher_B200>(false));
+
+    // leftover element-wise maps: dispatcher by schedule type, scheduler by target name, as register_cuda_plugin() does for
+    // "CUDA" / "cuda" (opt/include/sdfg/targets/cuda/plugin.h:21-34,119-120)
+    context.map_dispatcher_registry.register_map_dispatcher(
+        ScheduleType_B200::value(),
+        [](codegen::LanguageExtension& language_extension, StructuredSDFG& sdfg, analysis::AnalysisManager& analysis_manager,
+           structured_control_flow::Map& node, codegen::InstrumentationPlan& instrumentation_plan,
+           codegen::ArgCapturePlan& arg_capture_plan) {
+            return std::make_unique<B200MapDispatcher>(language_extension, sdfg, analysis_manager, node, instrumentation_plan,
+                                                       arg_capture_plan);
+        });
+    context.scheduler_registry.register_loop_scheduler<B200Scheduler>(B200Scheduler::target());
 
     // serializers of the two new nodes, so that dumps (python_program.py:283,301) round-trip
     auto& ser = context.library_node_serializer_registry;
