@@ -224,6 +224,23 @@ def make_workload(name, torch, ops, rank, world, strong=False):
                     config={"workload": f"GEMM {name[5:]} 8192^3, B as [N,K]", "l2": "operands (128-256 MB each) larger than L2"},
                     kind="gemm", replicas_only=True)
 
+    if name == "gemm_f32_exact":
+        # the same contraction with DOCC_B200_FLAG_FP32_EXACT: fp32 FMA arithmetic like the reference's loop nest, no tensor cores
+        n = 4096
+        g.manual_seed(6)
+        a = torch.randn(n, n, generator=g).to(dev)
+        b = torch.randn(n, n, generator=g).to(dev)
+        c = torch.empty(n, n, dtype=torch.float32, device=dev)
+
+        def step():
+            ops.gemm(a, b, c, transb=True, flags=ops.FLAG_FP32_EXACT)
+
+        return dict(step=step, units=2 * n ** 3, unit="TFLOP/s", scale=1e-12, metric="gemm_f32_exact_tflops", dtype="f32", bound="fma",
+                    peak=148 * 128 * 2 * 1.965e-3, peak_source="of the nominal FFMA rate, 148 SMs x 128 lanes x 2 x 1.965 GHz (no measured figure)",
+                    launches_per_step=1, flush=True,
+                    config={"workload": "GEMM fp32 4096^3 with FLAG_FP32_EXACT (FFMA kernel), B as [N,K]", "l2": "flushed between steps"},
+                    kind="gemm", replicas_only=True)
+
     # ---- sharded workloads -----------------------------------------------------------------------------
     # `strong`: ONE configuration is split over the ranks by a GatherPlan (chunk-major, rank order inside a chunk); the
     # rank's kernels write straight into its slices of the preallocated gathered buffer and the chunks' all-gathers
@@ -660,7 +677,7 @@ def main():
 
     if not args.no_extras and args.workload == "softmax":
         extras = []
-        names = ["gemm_f64", "gemm_bf16", "gemm_f32", "conv_f32", "conv_bf16", "attention", "attention_causal", "block_f32", "block_bf16"]
+        names = ["gemm_f64", "gemm_bf16", "gemm_f32", "gemm_f32_exact", "conv_f32", "conv_bf16", "attention", "attention_causal", "block_f32", "block_bf16"]
         for nm in names:
             try:
                 w2 = make_workload(nm, torch, ops, rank, world)
@@ -682,7 +699,7 @@ def main():
                     if cb:
                         ex["cpu_baseline"] = cb
                 # the split-and-gather reading of the sharded configurations, next to the weak one
-                if world > 1 and nm not in ("gemm_f64", "gemm_bf16", "gemm_f32"):
+                if world > 1 and nm not in ("gemm_f64", "gemm_bf16", "gemm_f32", "gemm_f32_exact"):
                     w3 = make_workload(nm, torch, ops, rank, world, strong=True)
                     ms3, _, _, comp3 = time_workload(w3, torch, dist, ops, args.extra_steps, 3, world, rank)
                     ex["split_gather"] = {

@@ -102,14 +102,32 @@ class GEMMNode(LibraryNode):
         if len(self.inputs) not in (2, 3):
             raise InvalidSDFGException("GEMMNode requires __A and __B (and optionally __C)")
 
-    def flop(self, env=None) -> Optional[int]:
-        # 2mnk + 2mn, GEMMNode::flop (gemm_node.cpp:337-356)
-        if env is None:
-            return None
+    def _mnk(self, env):
         a, b = env[self.inputs[0]], env[self.inputs[1]]
         m, k = (a.shape[1], a.shape[0]) if self.trans_a else a.shape
         n = b.shape[0] if self.trans_b else b.shape[1]
-        return 2 * m * n * k + 2 * m * n
+        return m, n, k
+
+    def flops(self, env, alpha_non_zero=True, alpha_non_ident=True, beta_non_zero=True, beta_non_ident=True) -> int:
+        """GEMMNode::flops (gemm_node.cpp:341-356): every term is multiplied by the condition it depends on.
+        mn*k multiplies and mn*(k-1) additions of the product if alpha != 0; mn multiplies for the alpha scaling if
+        alpha is neither 0 nor 1; mn multiplies for the beta scaling if beta is neither 0 nor 1; mn additions of the
+        scaled C if beta != 0."""
+        m, n, k = self._mnk(env)
+        res = m * n
+        mul_ops = res * k * int(alpha_non_zero) + res * int(alpha_non_ident and alpha_non_zero) + res * int(beta_non_ident and beta_non_zero)
+        add_ops = res * (k - 1) * int(alpha_non_zero) + res * int(beta_non_zero)
+        return mul_ops + add_ops
+
+    def flop(self, env=None) -> Optional[int]:
+        # GEMMNode::flop (gemm_node.cpp:337-339): all four conditions true, 2mnk + 2mn
+        if env is None:
+            return None
+        return self.flops(env)
+
+    def flop_for_constants(self, env) -> int:
+        """The count for this node's own alpha and beta (they are node constants here, so the conditions are known)."""
+        return self.flops(env, self.alpha != 0.0, self.alpha != 1.0, self.beta != 0.0, self.beta != 1.0)
 
     def _params(self) -> dict:
         return {"precision": self.precision, "layout": self.layout, "trans_a": self.trans_a, "trans_b": self.trans_b,

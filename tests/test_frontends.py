@@ -378,3 +378,29 @@ def test_compile_torch_entry_point(rt):
     x = torch.randn(8, 32)
     prog = docc_torch.compile_torch(model, x, target="cuda")
     assert torch.allclose(prog(x), model(x), rtol=1e-4, atol=1e-5)
+
+
+def test_gemm_flop_terms_follow_the_alpha_and_beta_conditions():
+    """GEMMNode::flops (gemm_node.cpp:341-356) multiplies each term by the condition it depends on; flop() is the
+    all-true case, 2mnk + 2mn."""
+    m, n, k = 7, 5, 3
+    env = {"a": np.zeros((m, k)), "b": np.zeros((k, n))}
+    g = nodes.GEMMNode(inputs=["a", "b"], outputs=["c"])
+    res = m * n
+    assert g.flop(env) == 2 * m * n * k + 2 * m * n
+    assert g.flop() is None
+    # alpha == 0: no product, no alpha scaling; the beta terms stay
+    assert g.flops(env, alpha_non_zero=False) == 2 * res
+    # alpha == 1: the product without the scaling multiply
+    assert g.flops(env, alpha_non_ident=False) == res * k + res * (k - 1) + 2 * res
+    # beta == 0: neither the scaling of C nor its addition
+    assert g.flops(env, beta_non_zero=False) == res * k + res * (k - 1) + res
+    # beta == 1: C is added unscaled
+    assert g.flops(env, beta_non_ident=False) == res * k + res * (k - 1) + res + res
+    # plain product (alpha 1, beta 0), the case the front ends emit: 2mnk - mn
+    plain = nodes.GEMMNode(inputs=["a", "b"], outputs=["c"], alpha=1.0, beta=0.0)
+    assert plain.flop_for_constants(env) == 2 * m * n * k - res
+    assert nodes.GEMMNode(inputs=["a", "b"], outputs=["c"], alpha=0.5, beta=2.0).flop_for_constants(env) == g.flop(env)
+    # transposed operands read their extents the other way round
+    env_t = {"a": np.zeros((k, m)), "b": np.zeros((n, k))}
+    assert nodes.GEMMNode(inputs=["a", "b"], outputs=["c"], trans_a=True, trans_b=True).flop(env_t) == g.flop(env)
