@@ -36,7 +36,8 @@ from docc_b200.sharding import GatherPlan  # noqa: E402
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from the ncu captures
 # (isolated launches: part of the write-back is still in L2 when the kernel ends, which is why the softmax figure is
 # below its 268 MB of algorithmic bytes)
-NCU_TRAFFIC_BYTES = {"softmax": 214.6e6, "gemm_bf16": 988.8e6, "conv_bf16": 19.5e6, "attention": 244.6e6}
+NCU_TRAFFIC_BYTES = {"softmax": 213.9e6, "gemm_bf16": 1001.2e6, "conv_bf16": 15.4e6, "conv_f32": 33.5e6, "attention": 245.2e6, "attention_causal": 249.9e6,
+                     "gemm_f64": 16.0e6}
 
 # Sharded workloads (conv, attention, encoder block) at N > 1 GPUs are read two ways. Weak (the headline `value`): every
 # GPU runs the whole configuration on its own data and nothing is exchanged. Split-and-gather (`--strong`, and the
@@ -686,7 +687,8 @@ def main():
                 ex = {"metric": w2["metric"], "value": pg * (1 if w2.get("replicas_only") else world),
                       "unit": w2["unit"], "ms_per_step": ms2, "dtype": w2["dtype"], "config": w2["config"],
                       "roofline": {"bound": w2["bound"], "achieved": pg, "peak": w2["peak"],
-                                   "frac": (pg / w2["peak"]) if w2["peak"] else None,
+                                   "frac": (pg / w2["peak"]) if w2["peak"] else None, "unit": w2["unit"],
+                                   "traffic": NCU_TRAFFIC_BYTES.get(nm),
                                    "peak_source": w2.get("peak_source", f"of {peaks['source']}")},
                       "gpu_launches": int(l2), "clocks": clk2}
                 del w2
