@@ -1120,7 +1120,8 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     const size_t halo_total = size_t(kHaloSlots) * size_t(p.r_max + p.kh - 1) * 8192;
     const size_t fixed = 8 * 4096 + 512 + 1024 + 512;
     const size_t rings = 227 * 1024 - halo_total - fixed;
-    int x_chunks = 4;
+    static const int x_chunks_env = [] { const char* e = getenv("DOCC_B200_CONV_XCHUNKS"); return e ? atoi(e) : 0; }();
+    int x_chunks = x_chunks_env >= 2 && x_chunks_env <= 8 ? x_chunks_env : 4;
     int w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
     if (w_stages < 3) {  // tall filters leave little room: a shallower input ring
         x_chunks = 2;
@@ -1173,7 +1174,9 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     {
         // 16-bit NCHW inputs of narrow images go through the kernel that reads them in place (TMA rules: rows of a
         // multiple of 16 bytes on a 16-byte aligned base; one 64-pixel box per row has to reach every column a tap reads)
-        const int fused_rmax = int(10 - q.kh) < 4 ? int(10 - q.kh) : 4;
+        static const int rmax_env = [] { const char* e = getenv("DOCC_B200_CONV_RMAX"); return e ? atoi(e) : 0; }();
+        int fused_rmax = int(10 - q.kh) < 4 ? int(10 - q.kh) : 4;
+        if (rmax_env >= 1 && rmax_env < fused_rmax) fused_rmax = rmax_env;
         static const int fused_mode = [] { const char* e = getenv("DOCC_B200_CONV_FUSED"); return e ? atoi(e) : 1; }();
         const bool reach = q.pad_w == 0 ? q.W <= 64 : (q.pad_w <= 8 && q.W <= 56);
         if (fused_mode && !split && q.W % 8 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && q.Wo + q.kw - 1 <= 64 && reach &&
