@@ -604,7 +604,43 @@ __device__ __forceinline__ void weight_relayout(const TIn* __restrict__ Wt, __nv
 // Requirements (checked by the host): 16-bit input, W % 8 == 0, X 16-byte aligned, Wo + kw - 1 <= 64,
 // pad_w <= 8 and W <= 56, or pad_w == 0 and W <= 64.
 // Warps: 0 weight producer, 1 UMMA issuer, 2-9 epilogue, 10-13 transposers, 14 input producer.
+//
+// WRES (3x3 filters, one channel block, at most 128 output channels): the weights stay on the SM for the whole kernel.
+// Streaming them costs every tile nine 16 KB blocks through a ring that shared memory keeps four deep, over an L2 latency
+// of about 3 k clocks: 6.8 k clocks per tile whatever its height (measured), a third of the kernel at three tiles per
+// CTA. Here taps 0-7 live in tensor-memory columns 0-255 (lane = output channel, one column = two consecutive channels;
+// A operand of tcgen05.mma taken from tensor memory) and tap 8 in a 16 KB shared-memory block (A from shared memory);
+// columns 256-511 hold two accumulators of two output rows each ([128 oc] x [2 x 64 pixel slots]). At start-up the
+// weight producer brings the nine blocks through a two-stage ring that borrows the epilogue's staging tiles (unused
+// until the first accumulator is full); warps 2-5 move each block's rows into tensor memory.
 constexpr int kFusedThreads = 480;
+constexpr uint32_t kResAccCol = 256;  // first accumulator column of the resident-weights variant
+constexpr uint32_t kResTmemTaps = 8;  // taps held in tensor memory; the ninth stays in shared memory
+
+// Four consecutive 16-deep k-steps of D[tmem] (+)= A[tmem] * B[smem]: A advances by 8 columns, B by `b_step`.
+__device__ __forceinline__ void umma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                               uint64_t b_step) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 rb;\n"
+        ".reg .b32 ra;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "setp.ne.b32 p, %3, 0;\n"  // the instruction descriptor is never zero: p = true
+        "add.u32 ra, %1, 8;\n"
+        "add.s64 rb, %2, %5;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], rb, %3, p;\n"
+        "add.u32 ra, ra, 8;\n"
+        "add.s64 rb, rb, %5;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], rb, %3, p;\n"
+        "add.u32 ra, ra, 8;\n"
+        "add.s64 rb, rb, %5;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], rb, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "l"(b_step)
+        : "memory");
+}
 constexpr uint32_t kChunkBytes = 64 * 64 * 2;  // one input row of a channel block
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
@@ -618,7 +654,7 @@ __device__ __forceinline__ void stmatrix_x4(uint32_t addr, const uint32_t (&r)[4
                  : "memory");
 }
 
-template <bool IS_BF16>
+template <bool IS_BF16, bool WRES>
 __global__ void __launch_bounds__(kFusedThreads, 1)
     conv_nchw_kernel(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmX,
                      const __grid_constant__ CUtensorMap tmY, const ConvKernelParams p) {
@@ -643,14 +679,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     auto tempty_bar = [&](uint32_t i) { return bars + 176u + 8u * i; };
     auto full_x = [&](uint32_t i) { return bars + 192u + 8u * i; };
     auto empty_x = [&](uint32_t i) { return bars + 256u + 8u * i; };
+    const uint32_t wres_bar = bars + 120u;  // WRES: taps 0-7 are in tensor memory (one arrival per loading warp)
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 320u - raw_addr));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == 0 && lane == 0) {
-        for (uint32_t i = 0; i < w_stages; i++) {
-            mbar_init(full_a(i), 1);
-            mbar_init(empty_a(i), 1);
+        if constexpr (WRES) {
+            // start-up ring of two stages (full_a / empty_a 0, 1: four loading warps release a stage), full_a(2): tap 8 resident
+            for (uint32_t i = 0; i < 3; i++) mbar_init(full_a(i), 1);
+            for (uint32_t i = 0; i < 2; i++) mbar_init(empty_a(i), 4);
+            mbar_init(wres_bar, 4);
+        } else {
+            for (uint32_t i = 0; i < w_stages; i++) {
+                mbar_init(full_a(i), 1);
+                mbar_init(empty_a(i), 1);
+            }
         }
         for (uint32_t i = 0; i < 2; i++) {
             mbar_init(full_h(i), 4);  // one arrival per transposer warp
@@ -698,7 +742,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 
     if (warp == 0) {
         // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
-        if (lane == 0) {
+        if (WRES && lane == 0) {
+            griddep_wait();  // the re-laid weights come from the launch before this one
+            // once: taps 0-7 through the two borrowed staging stages, tap 8 into its resident block
+            for (uint32_t tap = 0; tap < kResTmemTaps; tap++) {
+                const uint32_t st = tap & 1u;
+                if (!mbar_wait(empty_a(st), ((tap >> 1) & 1u) ^ 1u)) {
+                    conv_timeout(p.status, 31);
+                    break;
+                }
+                mbar_arrive_expect_tx(full_a(st), kABytes);
+                tma_load_2d(sStage + st * kABytes, &tmW0, full_a(st), int(tap) * p.C, 0);
+            }
+            mbar_arrive_expect_tx(full_a(2), kABytes);
+            tma_load_2d(sA, &tmW0, full_a(2), int(kResTmemTaps) * p.C, 0);
+        } else if (lane == 0) {
             griddep_wait();  // the re-laid weights come from the launch before this one
             uint32_t s = 0, ph = 0;
             long long u = u_begin;
@@ -773,6 +831,51 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             const uint64_t a_desc0 = make_smem_desc(sA, 16u, 1024u), h_desc0 = make_smem_desc(sH, 16u, 1024u);
             uint32_t s = 0, ph = 0, hs = 0, hph = 0;
             uint64_t a_desc = a_desc0;
+            if constexpr (WRES) {
+                if (!mbar_wait(wres_bar, 0) || !mbar_wait(full_a(2), 0)) {
+                    conv_timeout(p.status, 39);
+                    ok = false;
+                }
+                tc_fence_after();
+                uint32_t abuf = 0, aph = 0;
+                while (ok && next_tile(p, u, u_end, t)) {
+                    if (!mbar_wait(full_h(hs), hph)) {
+                        conv_timeout(p.status, 36);
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t slot_desc = h_desc0 + uint64_t(hs * (halo_bytes >> 4));
+                    for (int rr = 0; rr < t.rows && ok; rr += 2) {
+                        if (!mbar_wait(tempty_bar(abuf), aph ^ 1u)) {
+                            conv_timeout(p.status, 32);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        // two output rows per accumulator (one for the last row of an odd tile): 128 or 64 pixel slots
+                        const uint32_t idesc = make_idesc(128, (t.rows - rr >= 2) ? 128 : 64, 1, 0, 0);
+                        const uint32_t d_tmem = tmem_base + kResAccCol + abuf * 128u;
+                        const uint64_t row_desc = slot_desc + uint64_t(rr) * ((64 * 128) >> 4);
+#pragma unroll
+                        for (int tap = 0; tap < int(kResTmemTaps); tap++)
+                            umma_f16_ts_x4(d_tmem, tmem_base + uint32_t(tap) * 32u, row_desc + uint64_t(((tap / 3) * 64 + tap % 3) * 8), idesc,
+                                           tap ? 1u : 0u, 2);
+                        umma_f16_ss_x4<1>(d_tmem, a_desc0, row_desc + uint64_t((2 * 64 + 2) * 8), idesc, 1u, 2, 2);
+                        umma_commit(tfull_bar(abuf));
+                        if (++abuf == 2u) {
+                            abuf = 0;
+                            aph ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(empty_h(hs));
+                    if (++hs == uint32_t(kHaloSlots)) {
+                        hs = 0;
+                        hph ^= 1u;
+                    }
+                }
+                ok = false;  // done: the streamed-weights loop below is not for this variant
+            }
             while (ok && next_tile(p, u, u_end, t)) {
                 const uint32_t buf = lt & 1u, use = lt >> 1;
                 lt++;
@@ -900,25 +1003,73 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         Tile t;
         const long long plane = (long long)p.Ho * p.Wo;
         const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
-        while (next_tile(p, u, u_end, t)) {
+        if constexpr (WRES) {
+            // warps 2-5 (one per lane quadrant) move taps 0-7 from the start-up ring into tensor memory: thread = output
+            // channel, its 128-byte row of a block (16-byte chunk c at chunk c ^ (row & 7): the TMA swizzle, which also
+            // keeps the eight lanes of a quarter warp on different banks) becomes 32 columns
+            if (wg == 0) {
+                const uint32_t row = uint32_t(q * 32 + lane);
+                bool wok = true;
+                for (uint32_t tap = 0; tap < kResTmemTaps && wok; tap++) {
+                    const uint32_t st = tap & 1u;
+                    if (!mbar_wait(full_a(st), (tap >> 1) & 1u)) {
+                        if (lane == 0) conv_timeout(p.status, 40);
+                        wok = false;
+                        break;
+                    }
+                    uint32_t wv[32];
+                    const uint32_t rbase = sStage + st * kABytes + row * 128u;
+#pragma unroll
+                    for (uint32_t c = 0; c < 8; c++) {
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(wv[4 * c + 0]), "=r"(wv[4 * c + 1]), "=r"(wv[4 * c + 2]), "=r"(wv[4 * c + 3])
+                                     : "r"(rbase + ((c ^ (row & 7u)) << 4))
+                                     : "memory");
+                    }
+                    tmem_st_x32(tmem_base + (uint32_t(q * 32) << 16) + tap * 32u, wv);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_a(st));  // the rows of this stage are in registers: the producer may refill it
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0 && wok) mbar_arrive(wres_bar);
+            }
+        }
+        uint32_t abuf = 0, aph = 0;  // WRES: accumulator of the current pair of output rows
+        bool alive = true;
+        while (alive && next_tile(p, u, u_end, t)) {
             const uint32_t buf = lt & 1u, use = lt >> 1;
             lt++;
-            if (!mbar_wait(tfull_bar(buf), use & 1u)) {
-                if (lane == 0) conv_timeout(p.status, 34);
-                break;
+            if constexpr (!WRES) {
+                if (!mbar_wait(tfull_bar(buf), use & 1u)) {
+                    if (lane == 0) conv_timeout(p.status, 34);
+                    break;
+                }
+                tc_fence_after();
             }
-            tc_fence_after();
             const int oc = t.m0 + q * 32 + lane;
-            const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
+            uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + buf * 256u;
             const bool row_ok = oc < p.c_out;
             const float bv = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.f;
             // the two warps of a quadrant take alternate groups of 32 output pixels
             int gi = 0;
             for (int rr = 0; rr < t.rows; rr++) {
+                if constexpr (WRES) {
+                    if ((rr & 1) == 0) {  // a new accumulator every two rows
+                        if (!mbar_wait(tfull_bar(abuf), aph)) {
+                            if (lane == 0) conv_timeout(p.status, 34);
+                            alive = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        t_addr = tmem_base + (uint32_t(q * 32) << 16) + kResAccCol + abuf * 128u;
+                    }
+                }
                 float* yrow = p.Y + ((long long)t.n * p.c_out + (row_ok ? oc : 0)) * plane + (long long)(t.oh0 + rr) * p.Wo;
                 for (int c = 0; c < p.Wo; c += 32, gi++) {
                     if ((gi & 1) != wg) continue;
-                    const uint32_t col = uint32_t(rr * 64 + c);
+                    const uint32_t col = WRES ? uint32_t((rr & 1) * 64 + c) : uint32_t(rr * 64 + c);
                     if (p.tma_out) {
                         uint32_t r0[16], r1[16];
                         tmem_ld_x16(t_addr + col, r0);
@@ -959,10 +1110,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                         }
                     }
                 }
+                if constexpr (WRES) {
+                    if ((rr & 1) == 1 || rr == t.rows - 1) {  // the accumulator's rows are read: hand it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(tempty_bar(abuf));
+                        if (++abuf == 2u) {
+                            abuf = 0;
+                            aph ^= 1u;
+                        }
+                    }
+                }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(buf));
+            if constexpr (!WRES) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
+            }
         }
         if (p.tma_out && lane == 0) tma_store_wait<0>();
     }
@@ -1086,7 +1250,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
 
 bool g_conv_attr[16] = {false};
 bool g_halo_attr[16] = {false};
-bool g_fused_attr[16][2] = {};
+bool g_fused_attr[16][2][2] = {};
 
 // The fused path: weights re-laid by a small launch, then conv_nchw_kernel on the NCHW input in place.
 template <bool IS_BF16>
@@ -1121,21 +1285,31 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     const size_t fixed = 8 * 4096 + 512 + 1024 + 512;
     const size_t rings = 227 * 1024 - halo_total - fixed;
     static const int x_chunks_env = [] { const char* e = getenv("DOCC_B200_CONV_XCHUNKS"); return e ? atoi(e) : 0; }();
+    // resident weights: 3x3 filter, one channel block, one tile of output channels
+    static const int wres_mode = [] { const char* e = getenv("DOCC_B200_CONV_WRES"); return e ? atoi(e) : 1; }();
+    const bool wres = wres_mode && q.C == 64 && q.c_out <= 128 && q.kh == 3 && q.kw == 3;
     int x_chunks = x_chunks_env >= 2 && x_chunks_env <= 8 ? x_chunks_env : 4;
-    int w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
-    if (w_stages < 3) {  // tall filters leave little room: a shallower input ring
-        x_chunks = 2;
+    int w_stages;
+    if (wres) {
+        w_stages = 1;  // the block of tap 8
+        if (!(x_chunks_env >= 2 && x_chunks_env <= 8)) x_chunks = 8;  // the weight ring's room deepens the input ring
+        while (x_chunks > 2 && size_t(x_chunks) * kChunkBytes + kABytes > rings) x_chunks--;
+    } else {
         w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
+        if (w_stages < 3) {  // tall filters leave little room: a shallower input ring
+            x_chunks = 2;
+            w_stages = int((rings - size_t(x_chunks) * kChunkBytes) / kABytes);
+        }
+        if (w_stages > kMaxWStages) w_stages = kMaxWStages;
+        if (w_stages < 2) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: filter too tall for the fused kernel");
     }
-    if (w_stages > kMaxWStages) w_stages = kMaxWStages;
-    if (w_stages < 2) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: filter too tall for the fused kernel");
     p.w_stages = w_stages;
     p.x_chunks = x_chunks;
     const size_t smem = halo_total + size_t(w_stages) * kABytes + size_t(x_chunks) * kChunkBytes + fixed;
-    auto kern = conv_nchw_kernel<IS_BF16>;
-    if (!g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0]) {
+    auto kern = wres ? conv_nchw_kernel<IS_BF16, true> : conv_nchw_kernel<IS_BF16, false>;
+    if (!g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0][wres ? 1 : 0]) {
         DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0] = true;
+        g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0][wres ? 1 : 0] = true;
     }
     {
         const long long wblocks = ceil_div((long long)w_elems, 256 * 8);
