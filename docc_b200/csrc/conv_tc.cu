@@ -44,6 +44,7 @@ struct ConvKernelParams {
     int w_stages;  // halo variant: depth of the weight ring
     int x_chunks;  // fused variant: depth of the input staging ring
     int tma_out;  // Y rows are 16-byte aligned: full 32-pixel groups go out through TMA stores
+    int even_rows;  // tiles of an even number of rows where the range allows it (two-row accumulators)
     const float* bias;
     float* Y;
     DeviceStatus* status;
@@ -75,7 +76,8 @@ __device__ __forceinline__ bool next_tile(const ConvKernelParams& p, long long& 
     long long rem = p.Ho - t.oh0;
     if (rem > u_end - u) rem = u_end - u;
     const long long nt = (rem + p.r_max - 1) / p.r_max;
-    const long long r = (rem + nt - 1) / nt;
+    long long r = (rem + nt - 1) / nt;
+    if (p.even_rows && (r & 1) && r < rem && r < p.r_max) r++;
     t.rows = int(r);
     u += r;
     return true;
@@ -680,15 +682,24 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     auto full_x = [&](uint32_t i) { return bars + 192u + 8u * i; };
     auto empty_x = [&](uint32_t i) { return bars + 256u + 8u * i; };
     const uint32_t wres_bar = bars + 120u;  // WRES: taps 0-7 are in tensor memory (one arrival per loading warp)
+    // WRES start-up ring: the epilogue's staging tiles (two blocks of 16 KB, unused until the first accumulator is full)
+    // and as much of halo slot 1 as holds whole blocks (unused until the second tile is assembled; the transposers wait
+    // for wres_bar before they write there)
+    const uint32_t res_stages = 2u + (halo_bytes / kABytes < 3u ? halo_bytes / kABytes : 3u);
+    auto res_stage_addr = [&](uint32_t i) { return i < 2u ? sStage + i * kABytes : sH + halo_bytes + (i - 2u) * kABytes; };
+    const uint32_t res_full = bars + 56u;  // tap 8 is in its resident block
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 320u - raw_addr));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == 0 && lane == 0) {
         if constexpr (WRES) {
-            // start-up ring of two stages (full_a / empty_a 0, 1: four loading warps release a stage), full_a(2): tap 8 resident
-            for (uint32_t i = 0; i < 3; i++) mbar_init(full_a(i), 1);
-            for (uint32_t i = 0; i < 2; i++) mbar_init(empty_a(i), 4);
+            // start-up ring (full_a / empty_a 0..4: four loading warps release a stage), res_full: tap 8 resident
+            for (uint32_t i = 0; i < res_stages; i++) {
+                mbar_init(full_a(i), 1);
+                mbar_init(empty_a(i), 4);
+            }
+            mbar_init(res_full, 1);
             mbar_init(wres_bar, 4);
         } else {
             for (uint32_t i = 0; i < w_stages; i++) {
@@ -744,18 +755,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
         if (WRES && lane == 0) {
             griddep_wait();  // the re-laid weights come from the launch before this one
-            // once: taps 0-7 through the two borrowed staging stages, tap 8 into its resident block
+            // once: taps 0-7 through the borrowed stages, tap 8 into its resident block
+            uint32_t st = 0, use = 0;
             for (uint32_t tap = 0; tap < kResTmemTaps; tap++) {
-                const uint32_t st = tap & 1u;
-                if (!mbar_wait(empty_a(st), ((tap >> 1) & 1u) ^ 1u)) {
+                if (!mbar_wait(empty_a(st), (use & 1u) ^ 1u)) {
                     conv_timeout(p.status, 31);
                     break;
                 }
                 mbar_arrive_expect_tx(full_a(st), kABytes);
-                tma_load_2d(sStage + st * kABytes, &tmW0, full_a(st), int(tap) * p.C, 0);
+                tma_load_2d(res_stage_addr(st), &tmW0, full_a(st), int(tap) * p.C, 0);
+                if (++st == res_stages) {
+                    st = 0;
+                    use++;
+                }
             }
-            mbar_arrive_expect_tx(full_a(2), kABytes);
-            tma_load_2d(sA, &tmW0, full_a(2), int(kResTmemTaps) * p.C, 0);
+            mbar_arrive_expect_tx(res_full, kABytes);
+            tma_load_2d(sA, &tmW0, res_full, int(kResTmemTaps) * p.C, 0);
         } else if (lane == 0) {
             griddep_wait();  // the re-laid weights come from the launch before this one
             uint32_t s = 0, ph = 0;
@@ -832,7 +847,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             uint32_t s = 0, ph = 0, hs = 0, hph = 0;
             uint64_t a_desc = a_desc0;
             if constexpr (WRES) {
-                if (!mbar_wait(wres_bar, 0) || !mbar_wait(full_a(2), 0)) {
+                if (!mbar_wait(wres_bar, 0) || !mbar_wait(res_full, 0)) {
                     conv_timeout(p.status, 39);
                     ok = false;
                 }
@@ -934,6 +949,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         long long u = u_begin;
         Tile t;
         bool ok = true;
+        bool wres_seen = false;
         while (ok && next_tile(p, u, u_end, t)) {
             const int hrows = t.rows + p.kh - 1;
             for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
@@ -943,6 +959,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                     break;
                 }
                 const uint32_t slot = sH + hs * halo_bytes;
+                if constexpr (WRES) {
+                    // halo slot 1 lends its room to the start-up weight ring: not before the weights are in tensor memory
+                    if (hs == 1u && !wres_seen) {
+                        if (!mbar_wait(wres_bar, 0)) {
+                            if (lane == 0) conv_timeout(p.status, 41);
+                            ok = false;
+                            break;
+                        }
+                        wres_seen = true;
+                    }
+                }
                 for (int hr = 0; hr < hrows; hr++) {
                     if (!mbar_wait(full_x(xs), xph)) {
                         if (lane == 0) conv_timeout(p.status, 38);
@@ -1010,15 +1037,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if (wg == 0) {
                 const uint32_t row = uint32_t(q * 32 + lane);
                 bool wok = true;
+                uint32_t st = 0, use = 0;
                 for (uint32_t tap = 0; tap < kResTmemTaps && wok; tap++) {
-                    const uint32_t st = tap & 1u;
-                    if (!mbar_wait(full_a(st), (tap >> 1) & 1u)) {
+                    if (!mbar_wait(full_a(st), use & 1u)) {
                         if (lane == 0) conv_timeout(p.status, 40);
                         wok = false;
                         break;
                     }
                     uint32_t wv[32];
-                    const uint32_t rbase = sStage + st * kABytes + row * 128u;
+                    const uint32_t rbase = res_stage_addr(st) + row * 128u;
 #pragma unroll
                     for (uint32_t c = 0; c < 8; c++) {
                         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
@@ -1029,6 +1056,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                     tmem_st_x32(tmem_base + (uint32_t(q * 32) << 16) + tap * 32u, wv);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_a(st));  // the rows of this stage are in registers: the producer may refill it
+                    if (++st == res_stages) {
+                        st = 0;
+                        use++;
+                    }
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -1292,6 +1323,7 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     int w_stages;
     if (wres) {
         w_stages = 1;  // the block of tap 8
+        p.even_rows = 1;
         if (!(x_chunks_env >= 2 && x_chunks_env <= 8)) x_chunks = 8;  // the weight ring's room deepens the input ring
         while (x_chunks > 2 && size_t(x_chunks) * kChunkBytes + kABytes > rings) x_chunks--;
     } else {
