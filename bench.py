@@ -271,21 +271,33 @@ def make_workload(name, torch, ops, rank, world, strong=False):
             ops.call("docc_b200_conv", ops._prec(xv), ord("s"), 2, ops._arr(xv.shape), ops._arr((3, 3)), ops._arr((1, 1)),
                      ops._arr((1, 1, 1, 1)), ops._arr((1, 1)), 128, 1, ops._ptr(xv), ops._ptr(w), ops._ptr(bias), ops._ptr(yv), 0)
 
-        cargs = (ops._prec(x), ord("s"), 2, ops._arr(x.shape), ops._arr((3, 3)), ops._arr((1, 1)), ops._arr((1, 1, 1, 1)),
-                 ops._arr((1, 1)), 128, 1, ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops._ptr(y), 0)
+        flops = 2 * n_local * 128 * 56 * 56 * 64 * 9
+        common = dict(units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops",
+                      dtype="bf16" if name == "conv_bf16" else "f32(split-bf16x3)", bound="tensor",
+                      peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None, kind="conv")
+        wtext = f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)"
+        if plan:
+            return dict(step=None, config={"workload": wtext, "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True,
+                        plan=plan, full_out=y, gather_bytes=y.numel() * 4,
+                        chunk=lambda c, out: conv_call(plan.local_chunk(x, c), out), **common)
+        # Steps of 25-70 us: an event pair per step (what the L2 flush between steps needs) adds the events' own latency and
+        # a 2 us timestamp granularity to every step. Instead the steps run back to back over six input/output sets
+        # (64-77 MB each, 385-462 MB in all), so no step finds its input, or room for its output, in the 126 MB L2.
+        n_sets = 6
+        xs = [x] + [torch.randn_like(x, dtype=torch.float32).to(x.dtype) for _ in range(n_sets - 1)]
+        ys = [y] + [torch.empty_like(y) for _ in range(n_sets - 1)]
+        cargs = [(ops._prec(xi), ord("s"), 2, ops._arr(xi.shape), ops._arr((3, 3)), ops._arr((1, 1)), ops._arr((1, 1, 1, 1)),
+                  ops._arr((1, 1)), 128, 1, ops._ptr(xi), ops._ptr(w), ops._ptr(bias), ops._ptr(yi), 0) for xi, yi in zip(xs, ys)]
+        state = {"i": 0}
 
         def step():
-            ops.call("docc_b200_conv", *cargs)
-            return y
+            i = state["i"] % n_sets
+            state["i"] += 1
+            ops.call("docc_b200_conv", *cargs[i])
+            return ys[i]
 
-        flops = 2 * n_local * 128 * 56 * 56 * 64 * 9
-        return dict(step=step, units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops",
-                    dtype="bf16" if name == "conv_bf16" else "f32(split-bf16x3)", bound="tensor",
-                    peak=peaks["bf16_tflops"] / (1 if name == "conv_bf16" else 3), launches_per_step=None,
-                    config={"workload": f"conv2d {name[5:]} [32,64,56,56]*[128,64,3,3] s1 p1 (BASELINE config 3)",
-                            "batch_per_gpu": n_local, "l2": "flushed between steps"}, flush=True, kind="conv",
-                    plan=plan, full_out=y, gather_bytes=y.numel() * 4,
-                    chunk=(lambda c, out: conv_call(plan.local_chunk(x, c), out)) if plan else None)
+        return dict(step=step, config={"workload": wtext, "batch_per_gpu": n_local,
+                                       "l2": "inputs and outputs rotated over 6 buffer sets, larger than L2"}, **common)
 
     if name in ("attention", "attention_causal"):
         causal = name.endswith("causal")

@@ -612,12 +612,18 @@ __device__ __forceinline__ void weight_relayout(const TIn* __restrict__ Wt, __nv
 // of about 3 k clocks: 6.8 k clocks per tile whatever its height (measured), a third of the kernel at three tiles per
 // CTA. Here taps 0-7 live in tensor-memory columns 0-255 (lane = output channel, one column = two consecutive channels;
 // A operand of tcgen05.mma taken from tensor memory) and tap 8 in a 16 KB shared-memory block (A from shared memory);
-// columns 256-511 hold two accumulators of two output rows each ([128 oc] x [2 x 64 pixel slots]). At start-up the
-// weight producer brings the nine blocks through a two-stage ring that borrows the epilogue's staging tiles (unused
-// until the first accumulator is full); warps 2-5 move each block's rows into tensor memory.
+// columns 256-511 hold two accumulators of two output rows each ([128 oc] x [2 x 64 pixel slots]). The weights are taken
+// as the caller holds them, [oc][c][3][3]: no re-laid copy, no launch before this one. At start-up the weight producer
+// brings every output channel's 1152-byte row in eight pieces of 144 bytes (eight channels x nine taps; one TMA box of
+// [128 oc][72 elements], unswizzled: the 144-byte pitch keeps a quarter warp's 16-byte reads on different banks) through
+// a three-stage ring that borrows the epilogue's staging tiles (unused until the first accumulator is full) and halo
+// slot 1 (unused until the second tile is assembled); warps 2-5 (thread = output channel) pick, for every tap, the eight
+// channels out of their 144 bytes with byte permutes and store them as four tensor-memory columns (taps 0-7) or as
+// one 16-byte chunk of the shared-memory block in the UMMA's swizzled K-major layout (tap 8).
 constexpr int kFusedThreads = 480;
 constexpr uint32_t kResAccCol = 256;  // first accumulator column of the resident-weights variant
 constexpr uint32_t kResTmemTaps = 8;  // taps held in tensor memory; the ninth stays in shared memory
+constexpr uint32_t kResPieceBytes = 128 * 144;  // one start-up piece: eight channels x nine taps of 128 output channels
 
 // Four consecutive 16-deep k-steps of D[tmem] (+)= A[tmem] * B[smem]: A advances by 8 columns, B by `b_step`.
 __device__ __forceinline__ void umma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
@@ -685,21 +691,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     // WRES start-up ring: the epilogue's staging tiles (two blocks of 16 KB, unused until the first accumulator is full)
     // and as much of halo slot 1 as holds whole blocks (unused until the second tile is assembled; the transposers wait
     // for wres_bar before they write there)
-    const uint32_t res_stages = 2u + (halo_bytes / kABytes < 3u ? halo_bytes / kABytes : 3u);
-    auto res_stage_addr = [&](uint32_t i) { return i < 2u ? sStage + i * kABytes : sH + halo_bytes + (i - 2u) * kABytes; };
-    const uint32_t res_full = bars + 56u;  // tap 8 is in its resident block
+    const uint32_t res_stages = 1u + (halo_bytes / kResPieceBytes < 2u ? halo_bytes / kResPieceBytes : 2u);
+    auto res_stage_addr = [&](uint32_t i) { return i < 1u ? sStage : sH + halo_bytes + (i - 1u) * kResPieceBytes; };
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 320u - raw_addr));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == 0 && lane == 0) {
         if constexpr (WRES) {
-            // start-up ring (full_a / empty_a 0..4: four loading warps release a stage), res_full: tap 8 resident
+            // start-up ring (full_a / empty_a 0..2: four loading warps release a stage)
             for (uint32_t i = 0; i < res_stages; i++) {
                 mbar_init(full_a(i), 1);
                 mbar_init(empty_a(i), 4);
             }
-            mbar_init(res_full, 1);
             mbar_init(wres_bar, 4);
         } else {
             for (uint32_t i = 0; i < w_stages; i++) {
@@ -754,23 +758,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     if (warp == 0) {
         // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
         if (WRES && lane == 0) {
-            griddep_wait();  // the re-laid weights come from the launch before this one
-            // once: taps 0-7 through the borrowed stages, tap 8 into its resident block
+            // once: the eight 144-byte pieces of every output channel's row through the borrowed stages
             uint32_t st = 0, use = 0;
-            for (uint32_t tap = 0; tap < kResTmemTaps; tap++) {
+            for (uint32_t piece = 0; piece < 8; piece++) {
                 if (!mbar_wait(empty_a(st), (use & 1u) ^ 1u)) {
                     conv_timeout(p.status, 31);
                     break;
                 }
-                mbar_arrive_expect_tx(full_a(st), kABytes);
-                tma_load_2d(res_stage_addr(st), &tmW0, full_a(st), int(tap) * p.C, 0);
+                mbar_arrive_expect_tx(full_a(st), kResPieceBytes);
+                tma_load_2d(res_stage_addr(st), &tmW0, full_a(st), int(piece) * 72, 0);
                 if (++st == res_stages) {
                     st = 0;
                     use++;
                 }
             }
-            mbar_arrive_expect_tx(res_full, kABytes);
-            tma_load_2d(sA, &tmW0, res_full, int(kResTmemTaps) * p.C, 0);
         } else if (lane == 0) {
             griddep_wait();  // the re-laid weights come from the launch before this one
             uint32_t s = 0, ph = 0;
@@ -847,7 +848,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             uint32_t s = 0, ph = 0, hs = 0, hph = 0;
             uint64_t a_desc = a_desc0;
             if constexpr (WRES) {
-                if (!mbar_wait(wres_bar, 0) || !mbar_wait(res_full, 0)) {
+                if (!mbar_wait(wres_bar, 0)) {
                     conv_timeout(p.status, 39);
                     ok = false;
                 }
@@ -1031,37 +1032,62 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         const long long plane = (long long)p.Ho * p.Wo;
         const uint32_t stage_base = sStage + uint32_t(warp - 2) * 4096u;
         if constexpr (WRES) {
-            // warps 2-5 (one per lane quadrant) move taps 0-7 from the start-up ring into tensor memory: thread = output
-            // channel, its 128-byte row of a block (16-byte chunk c at chunk c ^ (row & 7): the TMA swizzle, which also
-            // keeps the eight lanes of a quarter warp on different banks) becomes 32 columns
+            // warps 2-5 (one per lane quadrant): thread = output channel. A piece holds channels 8g..8g+7 of all nine taps
+            // as 72 consecutive elements (element = channel * 9 + tap); channels 2j and 2j+1 of a tap are elements 18j + tap
+            // and 18j + 9 + tap of the piece.
             if (wg == 0) {
                 const uint32_t row = uint32_t(q * 32 + lane);
+                const uint32_t w_taddr = tmem_base + (uint32_t(q * 32) << 16);
                 bool wok = true;
                 uint32_t st = 0, use = 0;
-                for (uint32_t tap = 0; tap < kResTmemTaps && wok; tap++) {
+#pragma unroll 1
+                for (uint32_t piece = 0; piece < 8 && wok; piece++) {
                     if (!mbar_wait(full_a(st), use & 1u)) {
                         if (lane == 0) conv_timeout(p.status, 40);
                         wok = false;
                         break;
                     }
-                    uint32_t wv[32];
-                    const uint32_t rbase = res_stage_addr(st) + row * 128u;
+                    uint32_t win[36];
+                    const uint32_t rbase = res_stage_addr(st) + row * 144u;
 #pragma unroll
-                    for (uint32_t c = 0; c < 8; c++) {
+                    for (uint32_t i = 0; i < 9; i++) {
                         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                     : "=r"(wv[4 * c + 0]), "=r"(wv[4 * c + 1]), "=r"(wv[4 * c + 2]), "=r"(wv[4 * c + 3])
-                                     : "r"(rbase + ((c ^ (row & 7u)) << 4))
+                                     : "=r"(win[4 * i + 0]), "=r"(win[4 * i + 1]), "=r"(win[4 * i + 2]), "=r"(win[4 * i + 3])
+                                     : "r"(rbase + i * 16u)
                                      : "memory");
                     }
-                    tmem_st_x32(tmem_base + (uint32_t(q * 32) << 16) + tap * 32u, wv);
+#pragma unroll
+                    for (int tap = 0; tap < 9; tap++) {
+                        uint32_t col[4];
+#pragma unroll
+                        for (int jj = 0; jj < 4; jj++) {
+                            const int e0 = 18 * jj + tap, e1 = e0 + 9;
+                            const uint32_t sel = ((e0 & 1) ? 0x0032u : 0x0010u) | ((e1 & 1) ? 0x7600u : 0x5400u);
+                            uint32_t pair = __byte_perm(win[e0 >> 1], win[e1 >> 1], sel);
+                            if constexpr (!IS_BF16) {  // fp16 weights: the tensor cores run in bf16 (as the transposers convert the input)
+                                const __nv_bfloat162 bv = __float22bfloat162_rn(__half22float2(*reinterpret_cast<const __half2*>(&pair)));
+                                pair = *reinterpret_cast<const uint32_t*>(&bv);
+                            }
+                            col[jj] = pair;
+                        }
+                        if (tap < int(kResTmemTaps)) {
+                            tmem_st_x4(w_taddr + uint32_t(tap) * 32u + piece * 4u, col);
+                        } else {
+                            // tap 8: chunk `piece` of this channel's row in the block the UMMA reads (128-byte rows, 128-byte swizzle)
+                            const uint32_t dst = sA + row * 128u + ((piece ^ (row & 7u)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(col[0]), "r"(col[1]), "r"(col[2]), "r"(col[3])
+                                         : "memory");
+                        }
+                    }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(empty_a(st));  // the rows of this stage are in registers: the producer may refill it
+                    if (lane == 0) mbar_arrive(empty_a(st));  // the rows of this stage have been consumed: the producer may refill it
                     if (++st == res_stages) {
                         st = 0;
                         use++;
                     }
                 }
                 tmem_st_wait();
+                fence_proxy_async_smem();  // tap 8's block was written with generic stores; the tensor core reads it through the async proxy
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0 && wok) mbar_arrive(wres_bar);
@@ -1294,11 +1320,20 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
     CUtensorMap tm_w, tm_x, tm_y;
     memset(&tm_y, 0, sizeof(tm_y));
+    // resident weights: 3x3 filter, one channel block, one tile of output channels, weights read where they lie
+    static const int wres_mode = [] { const char* e = getenv("DOCC_B200_CONV_WRES"); return e ? atoi(e) : 1; }();
+    const bool wres = wres_mode && q.C == 64 && q.c_out <= 128 && q.kh == 3 && q.kw == 3 && reinterpret_cast<uintptr_t>(Wt) % 16 == 0;
     {
         const uint64_t wd[2] = {uint64_t(Kt), uint64_t(q.c_out)};
         const uint64_t ws[1] = {uint64_t(Kt) * 2};
-        const uint32_t wb[2] = {64, 128};
-        DOCC_TRY(encode_tmap_16bit(&tm_w, w_hi, 2, wd, ws, wb));
+        if (wres) {
+            // the caller's [oc][c][3][3] array as rows of 576 elements; a box is 72 elements (eight channels) of 128 rows
+            const uint32_t wb[2] = {72, 128};
+            DOCC_TRY(encode_tmap(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, CU_TENSOR_MAP_SWIZZLE_NONE, Wt, 2, wd, ws, wb));
+        } else {
+            const uint32_t wb[2] = {64, 128};
+            DOCC_TRY(encode_tmap_16bit(&tm_w, w_hi, 2, wd, ws, wb));
+        }
         // the input as it lies in memory: pixels, rows, channels, images; one box = one row of 64 channels
         const uint64_t xd[4] = {uint64_t(q.W), uint64_t(q.H), uint64_t(q.C), uint64_t(q.N)};
         const uint64_t xs[3] = {uint64_t(q.W) * 2, uint64_t(q.H * q.W) * 2, uint64_t(q.H * q.W) * q.C * 2};
@@ -1316,9 +1351,6 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     const size_t fixed = 8 * 4096 + 512 + 1024 + 512;
     const size_t rings = 227 * 1024 - halo_total - fixed;
     static const int x_chunks_env = [] { const char* e = getenv("DOCC_B200_CONV_XCHUNKS"); return e ? atoi(e) : 0; }();
-    // resident weights: 3x3 filter, one channel block, one tile of output channels
-    static const int wres_mode = [] { const char* e = getenv("DOCC_B200_CONV_WRES"); return e ? atoi(e) : 1; }();
-    const bool wres = wres_mode && q.C == 64 && q.c_out <= 128 && q.kh == 3 && q.kw == 3;
     int x_chunks = x_chunks_env >= 2 && x_chunks_env <= 8 ? x_chunks_env : 4;
     int w_stages;
     if (wres) {
@@ -1343,7 +1375,7 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
         DOCC_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         g_fused_attr[ctx->device & 15][IS_BF16 ? 1 : 0][wres ? 1 : 0] = true;
     }
-    {
+    if (!wres) {
         const long long wblocks = ceil_div((long long)w_elems, 256 * 8);
         if (wblocks > 0x7fffffff) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: weight tensor too large");
         const int vec_ok = reinterpret_cast<uintptr_t>(Wt) % 16 == 0 ? 1 : 0;
@@ -1362,7 +1394,7 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = wres ? 0 : 1;  // resident weights: no launch of ours precedes the kernel, so it must not start under its predecessor
     DOCC_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, p));
     return after_launch(ctx, "conv_nchw_kernel");
 }
