@@ -783,16 +783,33 @@ __global__ void __launch_bounds__(320, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_pairs = (p.n_qtiles + 1) / 2;
-    // work item = (batch, head, pair of query tiles); a CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ...
+    // work item = (batch, head, pair of query tiles). Without a mask every item costs the same and a CTA walks items
+    // blockIdx.x, blockIdx.x + gridDim.x, ... Under a causal mask an item's cost grows with its pair index, so the items are
+    // ordered heaviest first (all (batch, head) of the last pair, then of the pair before, ...) and dealt out in alternating
+    // direction (CTA c takes position c of the even rounds and position G - 1 - c of the odd ones), which gives every CTA
+    // about the same number of key blocks without any run-time scheduling.
     int q0[2], nb[2], n_max = 0, h = 0, b = 0;
+    const int n_bh = p.n_items / n_pairs;
+    auto item_of = [&](int k) {  // the CTA's k-th item, -1 when it has none left
+        const int G = int(gridDim.x);
+        const int pos = (p.causal && (k & 1)) ? G - 1 - int(blockIdx.x) : int(blockIdx.x);
+        const long long L = (long long)k * G + pos;
+        return L < p.n_items ? int(L) : -1;
+    };
     auto set_item = [&](int item) {
-        const int pair = item % n_pairs;
-        const int bh = item / n_pairs;
+        const int pair = p.causal ? n_pairs - 1 - item / n_bh : item % n_pairs;
+        const int bh = p.causal ? item % n_bh : item / n_pairs;
         h = bh % p.H;
         b = bh / p.H;
         for (int t = 0; t < 2; t++) {
             q0[t] = (pair * 2 + t) * kBQ;
-            nb[t] = q0[t] < p.Sq ? (p.Skv + kBKV - 1) / kBKV : 0;  // not used with a causal mask
+            int kv_end = p.Skv;
+            if (p.causal) {
+                const int last = q0[t] + kBQ - 1 + p.causal_off;  // last key visible to the last row of the tile
+                kv_end = last + 1 < p.Skv ? last + 1 : p.Skv;
+                if (kv_end < 0) kv_end = 0;
+            }
+            nb[t] = q0[t] < p.Sq ? (kv_end + kBKV - 1) / kBKV : 0;
         }
         n_max = nb[0] > nb[1] ? nb[0] : nb[1];
     };
@@ -834,7 +851,9 @@ __global__ void __launch_bounds__(320, 1)
           uint32_t ring = 0;          // ring entries issued so far (the ring runs on across items)
           uint32_t q_use[2] = {0, 0};  // items in which tile t was active so far
           bool alive = true;
-          for (int item = blockIdx.x; item < p.n_items && alive; item += gridDim.x) {
+          for (int k = 0; alive; k++) {
+            const int item = item_of(k);
+            if (item < 0) break;
             set_item(item);
             for (int t = 0; t < 2; t++) {
                 if (nb[t] == 0) continue;
@@ -898,7 +917,9 @@ __global__ void __launch_bounds__(320, 1)
                 product(q_hi, kb_hi);
                 umma_commit(s_full(t));
             };
-          for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+          for (int k = 0; ok; k++) {
+            const int item = item_of(k);
+            if (item < 0) break;
             set_item(item);
             for (int t = 0; t < 2 && ok; t++) {
                 if (nb[t] == 0) continue;
@@ -983,14 +1004,16 @@ __global__ void __launch_bounds__(320, 1)
         const uint32_t o_addr = lane_addr + 256u + uint32_t(t) * 128u;
         bool ok = true;
         uint32_t s_cnt = 0, o_cnt = 0;  // score blocks consumed / P V products awaited so far (all items)
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      for (int k = 0; ok; k++) {
+        const int item = item_of(k);
+        if (item < 0) break;
         set_item(item);
         const int row = q0[t] + r;
         const int n_t = nb[t];
         if (n_t == 0) continue;  // odd tile count: the second tile of the last pair does not exist
         float m = -INFINITY;  // maximum the stored exponentials are relative to
         float l = 0.f;
-        const int row_limit = p.Skv - 1;
+        const int row_limit = p.causal ? row + p.causal_off : p.Skv - 1;  // last visible key of this row
 
         for (int j = 0; j < n_t && ok; j++) {
             const int k0 = j * kBKV;
@@ -1001,7 +1024,7 @@ __global__ void __launch_bounds__(320, 1)
             }
             tc_fence_after();
             s_cnt++;
-            const bool need_mask = k0 + kBKV > p.Skv;
+            const bool need_mask = (k0 + kBKV > p.Skv) || (p.causal && k0 + kBKV - 1 > q0[t] + p.causal_off);
             const int visible = (row_limit < p.Skv - 1 ? row_limit : p.Skv - 1) - k0;
             // The block body exists twice, with and without masking: the mask test is uniform over the warp, and as a
             // run-time condition inside the loops it costs two compare/select instructions per score on every block.
@@ -1191,7 +1214,7 @@ int launch2(Ctx* ctx, const AttnProblem& p, const CUtensorMap* maps, const AttnK
     return after_launch(ctx, "attention_tc2_kernel");
 }
 
-// Persistent variant (no causal mask): one CTA per SM walks the work items, so tensor-memory allocation, barrier set-up,
+// Persistent variant: one CTA per SM walks the work items, so tensor-memory allocation, barrier set-up,
 // the first Q / K loads and the final store of O overlap the neighbouring items instead of costing every item its own
 // prologue and epilogue (with S = 512 an item is only four key blocks long).
 bool g_attr2p_done[16][6] = {};
@@ -1294,7 +1317,10 @@ int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, c
     const bool bf = p.prec == DOCC_B200_PREC_B;
     static const bool single_tile = [] { const char* e = getenv("DOCC_B200_ATTENTION_SINGLE_TILE"); return e && e[0] == '1'; }();
     static const bool persistent = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT"); return !e || e[0] != '0'; }();
-    if (!single_tile && p.Sq > kBQ && persistent && !p.causal) {
+    // under a causal mask the persistent walk needs every query row to see at least one key (Skv >= Sq)
+    static const bool persistent_causal = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT_CAUSAL"); return !e || e[0] != '0'; }();
+    const bool walk = persistent && (!p.causal || (persistent_causal && p.Skv >= p.Sq));
+    if (!single_tile && p.Sq > kBQ && walk) {
         const CUtensorMap maps[6] = {tq, tk, tv, tq, tk, tv};
         if (p.D == 128) return bf ? launch2p<128, true, false>(ctx, p, maps, kp, 0) : launch2p<128, false, false>(ctx, p, maps, kp, 1);
         return bf ? launch2p<64, true, false>(ctx, p, maps, kp, 2) : launch2p<64, false, false>(ctx, p, maps, kp, 3);
@@ -1356,7 +1382,8 @@ int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* 
     kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
     kp.status = ctx->status_dev;
     static const bool persistent = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT"); return !e || e[0] != '0'; }();
-    if (persistent && !p.causal && p.Sq > kBQ) return launch2p<64, true, true>(ctx, p, maps, kp, 4);
+    static const bool persistent_causal = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT_CAUSAL"); return !e || e[0] != '0'; }();
+    if (persistent && (!p.causal || (persistent_causal && p.Skv >= p.Sq)) && p.Sq > kBQ) return launch2p<64, true, true>(ctx, p, maps, kp, 4);
     return launch2<64, true, true>(ctx, p, maps, kp, 4);
 }
 

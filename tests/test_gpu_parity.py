@@ -415,9 +415,10 @@ def test_attention_fp32_cross_lengths(rt, causal):
 
 
 @pytest.mark.parametrize("causal", [False, True])
-@pytest.mark.parametrize("B,H,S,D", [(5, 16, 512, 64), (3, 20, 640, 128)])
+@pytest.mark.parametrize("B,H,S,D", [(5, 16, 512, 64), (3, 20, 640, 128), (9, 16, 768, 64)])
 def test_attention_bf16_persistent_walk(rt, B, H, S, D, causal):
-    # more (batch, head, tile pair) items than SMs: the persistent kernel's hand-over between items
+    # more (batch, head, tile pair) items than SMs: the persistent kernel's hand-over between items; under a causal mask the
+    # items are dealt heaviest first in alternating direction (two and three rounds here, odd tile counts included)
     torch.manual_seed(S)
     q, k, v = (torch.randn(B, H, S, D).bfloat16() for _ in range(3))
     ref = oracle.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), causal=causal)
