@@ -735,6 +735,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         }
         fence_barrier_init();
         prefetch_tensormap(&tmX);
+        // resident weights: the kernel is launched with programmatic stream serialization behind whatever ran before
+        // (nothing of ours precedes it), so every first touch of global memory waits for that launch to have completed
+        if constexpr (WRES) griddep_wait();
         long long u = u_begin;
         Tile t;
         if (next_tile(p, u, u_end, t)) {
@@ -754,6 +757,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    if constexpr (WRES) {
+        // barrier set-up, tensor-memory allocation and descriptor prefetch above overlap the tail of the launch before;
+        // the launch after this one may begin its own set-up as soon as SMs free up
+        griddep_wait();
+        griddep_launch_dependents();
+    }
 
     if (warp == 0) {
         // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
@@ -1394,7 +1403,7 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = wres ? 0 : 1;  // resident weights: no launch of ours precedes the kernel, so it must not start under its predecessor
+    cfg.numAttrs = 1;  // streamed weights: starts under conv_weights_kernel; resident weights: under whatever ran before (the kernel waits)
     DOCC_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, tm_y, p));
     return after_launch(ctx, "conv_nchw_kernel");
 }
