@@ -369,6 +369,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    // launched with programmatic stream serialization behind the re-layout launch: everything above overlaps its tail
+    griddep_wait();
+    griddep_launch_dependents();
 
     const long long u_begin = p.total_units * blockIdx.x / gridDim.x;
     const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
@@ -1248,6 +1251,9 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
     constexpr int PX = PAIR ? 128 : 64;
     __shared__ uint32_t tile_hi[PX][33];
     __shared__ uint32_t tile_lo[SPLIT ? PX : 1][33];
+    // may start under the launch before it (programmatic stream serialization): no global access before that one is complete
+    griddep_wait();
+    griddep_launch_dependents();
     if (blockIdx.y == gridDim.y - 1) {
         weight_relayout<TIn, SPLIT>(Wt, w_hi, w_lo, c_out, C, taps, (long long)blockIdx.z * gridDim.x + blockIdx.x, (long long)gridDim.x * gridDim.z);
         return;
@@ -1458,14 +1464,14 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
         dim3 grid(unsigned(ceil_div(HW, pair ? 128 : 64)), unsigned(q.C / 64 + 1), unsigned(q.N));
         if (grid.z > 65535) return set_error(DOCC_B200_ERR_UNSUPPORTED, "conv_tc: batch too large");
         if (split)
-            nchw_to_nhwc_kernel<float, true, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW,
-                                                                                  static_cast<const float*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
+            DOCC_CUDA_TRY(launch_pdl(nchw_to_nhwc_kernel<float, true, false>, grid, dim3(256), 0, ctx->stream, static_cast<const float*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                  static_cast<const float*>(Wt), w_hi, w_lo, int(q.c_out), int(taps)));
         else if (pair)
-            nchw_to_nhwc_kernel<__nv_bfloat16, false, true><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
-                                                                                          static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
+            DOCC_CUDA_TRY(launch_pdl(nchw_to_nhwc_kernel<__nv_bfloat16, false, true>, grid, dim3(256), 0, ctx->stream, static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                          static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps)));
         else
-            nchw_to_nhwc_kernel<__nv_bfloat16, false, false><<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
-                                                                                           static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps));
+            DOCC_CUDA_TRY(launch_pdl(nchw_to_nhwc_kernel<__nv_bfloat16, false, false>, grid, dim3(256), 0, ctx->stream, static_cast<const __nv_bfloat16*>(X), x_hi, x_lo, int(q.C), HW,
+                                                                                           static_cast<const __nv_bfloat16*>(Wt), w_hi, w_lo, int(q.c_out), int(taps)));
         DOCC_TRY(after_launch(ctx, "nchw_to_nhwc_kernel"));
     }
 
@@ -1534,7 +1540,7 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
         }
         long long grid_h = ceil_div(p.total_units, p.r_max);
         if (grid_h > ctx->sm_count) grid_h = ctx->sm_count;
-        conv_halo_kernel<<<unsigned(grid_h), kHaloThreads, smem_h, ctx->stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+        DOCC_CUDA_TRY(launch_pdl(conv_halo_kernel, dim3(unsigned(grid_h)), dim3(kHaloThreads), smem_h, ctx->stream, maps[0], maps[1], maps[2], maps[3], maps[4], p));
         return after_launch(ctx, "conv_halo_kernel");
     }
     const size_t smem = size_t(kStages) * (kABytes + kBBytes) + 4 * 4096 + 1024 + 256;
