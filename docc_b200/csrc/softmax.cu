@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "device_math.cuh"
+#include "ptx.cuh"
 
 namespace docc_b200 {
 namespace {
@@ -69,6 +70,10 @@ __global__ void __launch_bounds__(BLOCK) softmax_rows_kernel(const T* __restrict
     const int warp_in_row = t / 32;
     const int64_t packs_per_row = cols / VEC;  // cols % VEC == 0 is guaranteed by the dispatcher
     const int64_t n_groups = (rows + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+    // launched with programmatic stream serialization: blocks become resident while the launch before this one drains,
+    // and touch no global memory before it has completed
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
 
     for (int64_t g = blockIdx.x; g < n_groups; g += gridDim.x) {
         const int64_t row = g * ROWS_PER_BLOCK + r_in_block;
@@ -307,7 +312,7 @@ int launch_rows(Ctx* ctx, const T* X, T* Y, int64_t rows, int64_t cols) {
     // round of groups (5740 -> 5920 GB/s on fp32 [8192,4096]).
     const int64_t max_blocks = 0x7fffffff;
     const int grid = int(groups < max_blocks ? groups : max_blocks);
-    softmax_rows_kernel<T, VEC, VPT, TPR, BLOCK><<<grid, BLOCK, 0, ctx->stream>>>(X, Y, rows, cols);
+    DOCC_CUDA_TRY(launch_pdl(softmax_rows_kernel<T, VEC, VPT, TPR, BLOCK>, dim3(unsigned(grid)), dim3(BLOCK), 0, ctx->stream, X, Y, rows, cols));
     return after_launch(ctx, "softmax_rows_kernel");
 }
 
