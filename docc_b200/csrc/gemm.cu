@@ -10,6 +10,7 @@
 // a tiled FFMA kernel covers the rest (odd leading dimensions, DOCC_B200_FLAG_FP32_EXACT).
 #include "device_math.cuh"
 #include "gemm_tc.h"
+#include "ptx.cuh"
 
 namespace docc_b200 {
 namespace {
@@ -50,6 +51,9 @@ __global__ void __launch_bounds__(128) gemm_f64_dmma_kernel(const double* __rest
     A += blockIdx.z * g.a_bs;
     B += blockIdx.z * g.b_bs;
     C += blockIdx.z * g.c_bs;
+    // launched with programmatic stream serialization: no global access before the launch before this one has completed
+    ptx::griddep_wait();
+    ptx::griddep_launch_dependents();
 
     // global -> register staging; thread mapping follows whichever index is contiguous in memory
     const bool a_k_fast = g.a_cs == 1, b_n_fast = g.b_cs == 1;
@@ -232,8 +236,8 @@ int launch_dmma(Ctx* ctx, const void* A, const void* B, void* C, const GemmView&
     if (g.M == 0 || g.N == 0 || batch == 0) return DOCC_B200_OK;
     dim3 grid(unsigned(ceil_div(g.N, DN)), unsigned(ceil_div(g.M, DM)), unsigned(batch));
     if (grid.y > 65535 || grid.z > 65535) return set_error(DOCC_B200_ERR_UNSUPPORTED, "gemm: extent too large");
-    gemm_f64_dmma_kernel<<<grid, 128, 0, ctx->stream>>>(static_cast<const double*>(A), static_cast<const double*>(B),
-                                                         static_cast<double*>(C), g, alpha, beta);
+    DOCC_CUDA_TRY(launch_pdl(gemm_f64_dmma_kernel, grid, dim3(128), 0, ctx->stream, static_cast<const double*>(A), static_cast<const double*>(B),
+                             static_cast<double*>(C), g, alpha, beta));
     return after_launch(ctx, "gemm_f64_dmma_kernel");
 }
 
