@@ -336,7 +336,10 @@ def make_workload(name, torch, ops, rank, world, strong=False):
         return dict(step=step, units=flops, unit="TFLOP/s", scale=1e-12, metric=name + "_tflops", dtype="bf16",
                     bound="tensor", peak=peaks["bf16_tflops"], launches_per_step=1,
                     config={"workload": f"attention bf16 [8,16,2048,128] causal={causal} (BASELINE config 4)",
-                            "batch_per_gpu": b_local, "l2": "flushed between steps"}, flush=True, kind="attention",
+                            "batch_per_gpu": b_local,
+                            # Q, K, V and O are 67 MB each: one step's operands (268 MB) do not fit the 126 MB L2, so steps run back to back
+                            "l2": "flushed between steps" if plan else "operands of a step (268 MB) larger than L2"},
+                    flush=bool(plan), kind="attention",
                     plan=plan, full_out=o, gather_bytes=o.numel() * 2,
                     chunk=(lambda c, out: attn_call(plan.local_chunk(q, c), plan.local_chunk(k, c), plan.local_chunk(v, c), out))
                     if plan else None)
@@ -379,8 +382,10 @@ def make_workload(name, torch, ops, rank, world, strong=False):
                     dtype="bf16" if bf else "f32(split-bf16x3)", bound="tensor",
                     peak=peaks["bf16_tflops_sustained"] / (1 if bf else 3), launches_per_step=None,
                     config={"workload": f"pre-LN encoder block {'bf16' if bf else 'fp32'} d1024 h16 ff4096 [32,512,1024] "
-                                        "(BASELINE config 5)", "batch_per_gpu": b_local, "l2": "flushed between steps"},
-                    flush=True, kind="block", plan=plan, full_out=y, gather_bytes=y.numel() * y.element_size(),
+                                        "(BASELINE config 5)", "batch_per_gpu": b_local,
+                            # a step streams its 33-67 MB input, 25-50 MB of weights and 370-740 MB of intermediates through L2
+                            "l2": "flushed between steps" if plan else "working set of a step (over 400 MB) larger than L2"},
+                    flush=bool(plan), kind="block", plan=plan, full_out=y, gather_bytes=y.numel() * y.element_size(),
                     chunk=(lambda c, out: block_call(plan.local_chunk(x, c), out)) if plan else None)
 
     raise SystemExit(f"unknown workload {name}")
