@@ -3,8 +3,10 @@
 // docc's expansion of ConvNode (conv_node.cpp:243-399) gives every output element its own
 // sequential C_in*kh*kw FMA chain. Here, per image,  Y_n[oc, pixel] = sum_{tap, c} W[oc, tap, c] *
 // X_n[pixel + tap, c]  is a GEMM with M = C_out, N = output pixels, K = kh*kw*C_in:
-//   1. one launch re-lays X from NCHW to NHWC 16-bit (fp32 input: bf16 hi and lo planes) and W from
-//      [oc][c][kh][kw] to [oc][kh][kw][c], so that K is contiguous for both operands;
+//   1. fp32 inputs: one launch re-lays X from NCHW to NHWC 16-bit (bf16 hi and lo planes) and W from
+//      [oc][c][kh][kw] to [oc][kh][kw][c], so that K is contiguous for both operands. 16-bit inputs of narrow images
+//      skip this: conv_nchw_kernel reads the NCHW input in place and transposes it in shared memory (and, for 3x3
+//      filters over one channel block, takes the weights as they lie and keeps them on the SM);
 //   2. a persistent warp-specialised kernel (same skeleton as the GEMM engine: TMA producer warp,
 //      UMMA issuer warp, epilogue warps, two TMEM accumulators) walks tiles of 128 output channels
 //      x up to four output rows. Narrow images (conv_halo_kernel): the tile's input neighbourhood is
@@ -1330,14 +1332,14 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     using TIn = typename std::conditional<IS_BF16, __nv_bfloat16, __half>::type;
     const int64_t taps = q.kh * q.kw, Kt = taps * q.C;
     const size_t w_elems = size_t(q.c_out) * Kt;
-    void* ww;
-    DOCC_TRY(get_workspace(ctx, 1, w_elems * 2 + 256, &ww));
-    __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
-    CUtensorMap tm_w, tm_x, tm_y;
-    memset(&tm_y, 0, sizeof(tm_y));
     // resident weights: 3x3 filter, one channel block, one tile of output channels, weights read where they lie
     static const int wres_mode = [] { const char* e = getenv("DOCC_B200_CONV_WRES"); return e ? atoi(e) : 1; }();
     const bool wres = wres_mode && q.C == 64 && q.c_out <= 128 && q.kh == 3 && q.kw == 3 && reinterpret_cast<uintptr_t>(Wt) % 16 == 0;
+    void* ww = nullptr;
+    if (!wres) DOCC_TRY(get_workspace(ctx, 1, w_elems * 2 + 256, &ww));  // the re-laid copy of the streamed form
+    __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
+    CUtensorMap tm_w, tm_x, tm_y;
+    memset(&tm_y, 0, sizeof(tm_y));
     {
         const uint64_t wd[2] = {uint64_t(Kt), uint64_t(q.c_out)};
         const uint64_t ws[1] = {uint64_t(Kt) * 2};
