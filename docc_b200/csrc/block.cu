@@ -11,9 +11,11 @@
 namespace docc_b200 {
 
 int linear_device(Ctx* ctx, int prec, int64_t M, int64_t N, int64_t K, const void* X, int64_t ldx, const void* W, int64_t ldw,
-                  const float* bias, int act, const void* residual, int64_t ldr, void* Y, int64_t ldy);
+                  const float* bias, int act, const void* residual, int64_t ldr, void* Y, int64_t ldy, bool x_presplit = false);
 int attention_device(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, const void* V, void* O, int flags);
 int layernorm_f32(Ctx* ctx, int64_t rows, int64_t cols, const float* X, const float* g, const float* b, double eps, float* Y);
+int layernorm_f32_split(Ctx* ctx, int64_t rows, int64_t cols, const float* X, const float* g, const float* b, double eps,
+                        __nv_bfloat16* hi, __nv_bfloat16* lo);
 int layernorm_bf16(Ctx* ctx, int64_t rows, int64_t cols, const __nv_bfloat16* X, const float* g, const float* b, double eps,
                    __nv_bfloat16* Y);
 
@@ -40,9 +42,26 @@ int block_device(Ctx* ctx, int prec, const docc_b200_block_params& p, const void
     void* h2 = base + size_t(T) * 6 * d * es;
     void* f = base + size_t(T) * 7 * d * es;
 
-    DOCC_TRY(layernorm_any(ctx, prec, T, d, X, p.ln1_g, p.ln1_b, p.eps, h1));
+    // fp32: a LayerNorm that feeds a linear layer writes the GEMM's bf16 hi / lo operand planes itself (workspace slot 0,
+    // where the GEMM would put them: same size request, same pointer), which saves the split pass over the activations.
+    // Returns true when the planes are in place, false when the shape is not one the fused kernel takes.
+    auto ln_into_planes = [&](const void* src, const void* g, const void* b, bool* fused) -> int {
+        *fused = false;
+        if (prec != DOCC_B200_PREC_S || d % 8 != 0) return DOCC_B200_OK;
+        void* planes;
+        DOCC_TRY(get_workspace(ctx, 0, size_t(T) * size_t(d) * 2 * sizeof(__nv_bfloat16), &planes));
+        __nv_bfloat16* hi = static_cast<__nv_bfloat16*>(planes);
+        const int st = layernorm_f32_split(ctx, T, d, static_cast<const float*>(src), static_cast<const float*>(g),
+                                           static_cast<const float*>(b), p.eps, hi, hi + size_t(T) * size_t(d));
+        if (st == DOCC_B200_ERR_UNSUPPORTED) return DOCC_B200_OK;
+        *fused = st == DOCC_B200_OK;
+        return st;
+    };
+    bool fused = false;
+    DOCC_TRY(ln_into_planes(X, p.ln1_g, p.ln1_b, &fused));
+    if (!fused) DOCC_TRY(layernorm_any(ctx, prec, T, d, X, p.ln1_g, p.ln1_b, p.eps, h1));
     DOCC_TRY(linear_device(ctx, prec, T, 3 * d, d, h1, d, p.w_qkv, d, static_cast<const float*>(p.b_qkv), DOCC_B200_ACT_NONE,
-                           nullptr, 0, qkv, 3 * d));
+                           nullptr, 0, qkv, 3 * d, fused));
     AttnProblem a;
     a.prec = prec; a.B = p.batch; a.H = p.n_heads; a.Sq = p.seq; a.Skv = p.seq; a.D = dh;
     a.scale = 1.0f / sqrtf(float(dh)); a.causal = 0;
@@ -51,9 +70,10 @@ int block_device(Ctx* ctx, int prec, const docc_b200_block_params& p, const void
     const char* q = static_cast<const char*>(qkv);
     DOCC_TRY(attention_device(ctx, a, q, q + size_t(d) * es, q + size_t(2 * d) * es, att, 0));
     DOCC_TRY(linear_device(ctx, prec, T, d, d, att, d, p.w_o, d, static_cast<const float*>(p.b_o), DOCC_B200_ACT_NONE, X, d, h, d));
-    DOCC_TRY(layernorm_any(ctx, prec, T, d, h, p.ln2_g, p.ln2_b, p.eps, h2));
+    DOCC_TRY(ln_into_planes(h, p.ln2_g, p.ln2_b, &fused));
+    if (!fused) DOCC_TRY(layernorm_any(ctx, prec, T, d, h, p.ln2_g, p.ln2_b, p.eps, h2));
     DOCC_TRY(linear_device(ctx, prec, T, dff, d, h2, d, p.w_1, d, static_cast<const float*>(p.b_1), DOCC_B200_ACT_GELU_ERF, nullptr,
-                           0, f, dff));
+                           0, f, dff, fused));
     DOCC_TRY(linear_device(ctx, prec, T, d, dff, f, dff, p.w_2, dff, static_cast<const float*>(p.b_2), DOCC_B200_ACT_NONE, h, d, Y, d));
     return DOCC_B200_OK;
 }

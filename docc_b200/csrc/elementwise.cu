@@ -3,6 +3,8 @@
 // (elementwise_node.cpp:86-339 expanded and scheduled by cuda_map_dispatcher.cpp:42-333),
 // one HBM round trip per primitive. Here each call is one pass: every input byte is read once
 // with 128-bit accesses and every output byte written once.
+#include <type_traits>
+
 #include "common.cuh"
 #include "device_math.cuh"
 #include "ptx.cuh"
@@ -119,10 +121,14 @@ __global__ void __launch_bounds__(BLOCK) layernorm_kernel(const T* __restrict__ 
 constexpr int kLnStages = 3;
 constexpr int kLnWarps = 16;
 
+// `hi` / `lo` (fp32 rows only): instead of Y the kernel writes the result as two bf16 planes, value = hi + lo to about 16
+// mantissa bits, the form in which the fp32 tensor-core GEMM takes its operands; a LayerNorm that feeds a linear layer
+// then saves that GEMM's split pass over the activations (one read and one write of the fp32 tensor).
 template <typename T, int VPT>
 __global__ void __launch_bounds__(kLnWarps * 32, 1) layernorm_bulk_kernel(const T* __restrict__ X, const float* __restrict__ gamma,
                                                                          const float* __restrict__ beta, float eps, T* __restrict__ Y,
-                                                                         int64_t rows, int64_t cols) {
+                                                                         int64_t rows, int64_t cols, __nv_bfloat16* __restrict__ hi,
+                                                                         __nv_bfloat16* __restrict__ lo) {
     constexpr int VEC = 16 / sizeof(T);
     using P = Pack<T, VEC>;
     extern __shared__ __align__(128) uint8_t ln_smem[];
@@ -223,6 +229,19 @@ __global__ void __launch_bounds__(kLnWarps * 32, 1) layernorm_bulk_kernel(const 
                     pk.v[q4 * 4 + 2] = from_float<T>((to_float(cur[i].v[q4 * 4 + 2]) - mean) * rstd * g4.z + b4.z);
                     pk.v[q4 * 4 + 3] = from_float<T>((to_float(cur[i].v[q4 * 4 + 3]) - mean) * rstd * g4.w + b4.w);
                 }
+                if constexpr (std::is_same<T, float>::value) {
+                    if (hi) {  // VEC == 4: four values -> 8 bytes of each plane
+                        __nv_bfloat16 h[4], l[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            h[e] = __float2bfloat16_rn(pk.v[e]);
+                            l[e] = __float2bfloat16_rn(pk.v[e] - __bfloat162float(h[e]));
+                        }
+                        *reinterpret_cast<uint2*>(hi + row * cols + p * 4) = *reinterpret_cast<const uint2*>(h);
+                        *reinterpret_cast<uint2*>(lo + row * cols + p * 4) = *reinterpret_cast<const uint2*>(l);
+                        continue;
+                    }
+                }
                 store_pack(yr + p, pk);
             }
         }
@@ -253,7 +272,8 @@ __global__ void __launch_bounds__(256) layernorm_generic_kernel(const T* __restr
 }
 
 template <typename T, int VPT>
-int launch_ln_bulk(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols) {
+int launch_ln_bulk(Ctx* ctx, const T* X, const float* g, const float* b, float eps, T* Y, int64_t rows, int64_t cols,
+                   __nv_bfloat16* hi = nullptr, __nv_bfloat16* lo = nullptr) {
     static bool attr_done[16] = {};  // per instantiation and device
     const size_t row_pitch = (size_t(cols) * sizeof(T) + 127) & ~size_t(127);
     const size_t smem = ((size_t(cols) * 8 + 127) & ~size_t(127)) + ((size_t(kLnWarps * kLnStages) * 8 + 127) & ~size_t(127)) +
@@ -265,7 +285,7 @@ int launch_ln_bulk(Ctx* ctx, const T* X, const float* g, const float* b, float e
     }
     int64_t blocks = ceil_div(rows, kLnWarps);
     if (blocks > ctx->sm_count) blocks = ctx->sm_count;
-    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(blocks)), dim3(kLnWarps * 32), smem, ctx->stream, X, g, b, eps, Y, rows, cols));
+    DOCC_CUDA_TRY(launch_pdl(kern, dim3(unsigned(blocks)), dim3(kLnWarps * 32), smem, ctx->stream, X, g, b, eps, Y, rows, cols, hi, lo));
     return after_launch(ctx, "layernorm_bulk_kernel");
 }
 
@@ -438,6 +458,20 @@ int with_transfers(Ctx* ctx, const Staged& s, F fn) {
 // Used by the transformer block.
 int layernorm_f32(Ctx* ctx, int64_t rows, int64_t cols, const float* X, const float* g, const float* b, double eps, float* Y) {
     return layernorm_device<float>(ctx, rows, cols, X, g, b, eps, Y);
+}
+// fp32 LayerNorm whose result leaves as bf16 hi / lo planes of row pitch `cols` (see layernorm_bulk_kernel). Only the
+// many-rows kernel has this form: DOCC_B200_ERR_UNSUPPORTED tells the caller to normalise into fp32 and split as usual.
+int layernorm_f32_split(Ctx* ctx, int64_t rows, int64_t cols, const float* X, const float* g, const float* b, double eps,
+                        __nv_bfloat16* hi, __nv_bfloat16* lo) {
+    const bool aligned = cols % 8 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0 && reinterpret_cast<uintptr_t>(g) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(b) % 16 == 0 && reinterpret_cast<uintptr_t>(hi) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(lo) % 16 == 0;
+    const int64_t packs = cols / 4;
+    const bool many = rows >= int64_t(ctx->sm_count) * kLnWarps * 2 && size_t(cols) * 4 <= 4096;
+    if (!aligned || !many || packs <= 32) return DOCC_B200_ERR_UNSUPPORTED;
+    if (packs <= 64) return launch_ln_bulk<float, 2>(ctx, X, g, b, float(eps), nullptr, rows, cols, hi, lo);
+    if (packs <= 128) return launch_ln_bulk<float, 4>(ctx, X, g, b, float(eps), nullptr, rows, cols, hi, lo);
+    return launch_ln_bulk<float, 8>(ctx, X, g, b, float(eps), nullptr, rows, cols, hi, lo);
 }
 int layernorm_bf16(Ctx* ctx, int64_t rows, int64_t cols, const __nv_bfloat16* X, const float* g, const float* b, double eps,
                    __nv_bfloat16* Y) {

@@ -245,7 +245,10 @@ int64_t round_up8(int64_t v) { return (v + 7) / 8 * 8; }
 
 // fp32 / 16-bit GEMM on the tcgen05 engine. Row-major views only (column-major problems are
 // transposed by the caller). Returns DOCC_B200_ERR_UNSUPPORTED when the engine cannot take it.
-int run_tc(Ctx* ctx, int prec, const void* A, const void* B, const GemmView& g, int64_t batch, const TcEpilogue& ep) {
+// `a_presplit` (fp32, K-major A, one batch): the caller has already written the bf16 hi / lo planes of A into workspace
+// slot 0 in the layout below ([M][round_up8(K)], lo behind hi); A itself is not read.
+int run_tc(Ctx* ctx, int prec, const void* A, const void* B, const GemmView& g, int64_t batch, const TcEpilogue& ep,
+           bool a_presplit = false) {
     if (g.K == 0) return set_error(DOCC_B200_ERR_UNSUPPORTED, "K == 0");
     const bool a_kmajor = g.a_cs == 1;  // op(A)[i][k] contiguous in k
     const bool b_kmajor = g.b_rs == 1;  // op(B)[k][j] contiguous in k
@@ -271,7 +274,9 @@ int run_tc(Ctx* ctx, int prec, const void* A, const void* B, const GemmView& g, 
     __nv_bfloat16* b_hi = static_cast<__nv_bfloat16*>(wb);
     __nv_bfloat16* b_lo = b_hi + b_elems * b_planes;
     // A as stored: k-major -> [M][K] rows; otherwise memory is [K][M] and is transposed into [M][K]
-    if (a_kmajor) DOCC_TRY(split_f32_to_bf16x2(ctx, static_cast<const float*>(A), g.M, g.K, g.a_rs, a_planes, g.a_bs, false, a_hi, a_lo, kp, int64_t(a_elems)));
+    if (a_presplit) {
+        if (!a_kmajor || batch != 1) return set_error(DOCC_B200_ERR_INVALID_ARG, "gemm: pre-split A needs a K-major operand and one batch");
+    } else if (a_kmajor) DOCC_TRY(split_f32_to_bf16x2(ctx, static_cast<const float*>(A), g.M, g.K, g.a_rs, a_planes, g.a_bs, false, a_hi, a_lo, kp, int64_t(a_elems)));
     else DOCC_TRY(split_f32_to_bf16x2(ctx, static_cast<const float*>(A), g.K, g.M, g.a_cs, a_planes, g.a_bs, true, a_hi, a_lo, kp, int64_t(a_elems)));
     if (b_kmajor) DOCC_TRY(split_f32_to_bf16x2(ctx, static_cast<const float*>(B), g.N, g.K, g.b_cs, b_planes, g.b_bs, false, b_hi, b_lo, kp, int64_t(b_elems)));
     else DOCC_TRY(split_f32_to_bf16x2(ctx, static_cast<const float*>(B), g.K, g.N, g.b_rs, b_planes, g.b_bs, true, b_hi, b_lo, kp, int64_t(b_elems)));
@@ -296,6 +301,7 @@ struct GemmCall {
     const void* residual;
     int64_t ldr;
     int flags;
+    bool a_presplit = false;  // fp32 only: A's bf16 planes are already in workspace slot 0 (run_tc)
 };
 
 // Device-pointer GEMM on a row-major view.
@@ -314,9 +320,10 @@ int gemm_device(Ctx* ctx, const GemmCall& c, const void* A, const void* B, void*
         ep.bias = static_cast<const float*>(c.bias); ep.bias_mode = c.bias ? 1 : 0; ep.act = c.act;
         ep.residual = c.residual; ep.ldr = c.ldr; ep.residual_batch_stride = g.c_bs;
         ep.out = C; ep.ldo = g.ldc; ep.out_batch_stride = g.c_bs; ep.out_prec = c.prec;
-        int s = run_tc(ctx, c.prec, A, B, g, c.batch, ep);
+        int s = run_tc(ctx, c.prec, A, B, g, c.batch, ep, c.a_presplit);
         if (s != DOCC_B200_ERR_UNSUPPORTED) return s;
     }
+    if (c.a_presplit) return set_error(DOCC_B200_ERR_UNSUPPORTED, "gemm: pre-split A has no fallback off the tensor-core path");
     return launch_simt_prec(ctx, c.prec, A, B, C, g, sep, c.batch);
 }
 
@@ -373,8 +380,9 @@ double read_scalar(int prec, const void* p, double dflt) {
 
 // Used by the transformer block and conv: device-pointer linear layer Y = act(X W^T + bias) + residual.
 int linear_device(Ctx* ctx, int prec, int64_t M, int64_t N, int64_t K, const void* X, int64_t ldx, const void* W, int64_t ldw,
-                  const float* bias, int act, const void* residual, int64_t ldr, void* Y, int64_t ldy) {
+                  const float* bias, int act, const void* residual, int64_t ldr, void* Y, int64_t ldy, bool x_presplit) {
     GemmCall c;
+    c.a_presplit = x_presplit;
     c.prec = prec;
     c.g = GemmView{M, N, K, ldx, 1, 1, ldw, ldy, 0, 0, 0};
     c.batch = 1; c.alpha = 1.0; c.beta = 0.0; c.bias = bias; c.act = act; c.residual = residual; c.ldr = ldr; c.flags = 0;
