@@ -37,6 +37,8 @@ struct AttnKernelParams {
     float scale_log2;  // scale * log2(e)
     void* O;
     long long os_b, os_h, os_s;
+    void* O_hi;  // persistent fp32 kernel: when set, O leaves as bf16 hi / lo planes (same strides) instead of fp32
+    void* O_lo;
     DeviceStatus* status;
 };
 
@@ -1159,7 +1161,25 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
                     for (int i = 0; i < 32; i++) o[i] = 0u;
                 }
-                if (row < p.Sq && SPLIT) {
+                if (row < p.Sq && SPLIT && p.O_hi) {
+                    // the out-projection's operand planes: 32 values -> 64 bytes of each plane
+                    const long long off = b * p.os_b + h * p.os_h + (long long)row * p.os_s + c * 32;
+                    uint4* ph = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.O_hi) + off);
+                    uint4* pl = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.O_lo) + off);
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; v8++) {
+                        uint32_t wh[4], wl[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float x0 = __uint_as_float(o[v8 * 8 + 2 * e]) * inv, x1 = __uint_as_float(o[v8 * 8 + 2 * e + 1]) * inv;
+                            wh[e] = pack2<true>(x0, x1);
+                            const float h0 = __uint_as_float(wh[e] << 16), h1 = __uint_as_float(wh[e] & 0xffff0000u);
+                            wl[e] = pack2<true>(x0 - h0, x1 - h1);
+                        }
+                        ph[v8] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                        pl[v8] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                    }
+                } else if (row < p.Sq && SPLIT) {
 #pragma unroll
                     for (int v4 = 0; v4 < 8; v4++) {
                         float4 w;
@@ -1313,6 +1333,7 @@ int attention_tc(Ctx* ctx, const AttnProblem& p, const void* Q, const void* K, c
     kp.causal_off = int(p.Skv - p.Sq);
     kp.scale_log2 = p.scale * 1.4426950408889634f;
     kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
+    kp.O_hi = nullptr; kp.O_lo = nullptr;
     kp.status = ctx->status_dev;
     const bool bf = p.prec == DOCC_B200_PREC_B;
     static const bool single_tile = [] { const char* e = getenv("DOCC_B200_ATTENTION_SINGLE_TILE"); return e && e[0] == '1'; }();
@@ -1380,10 +1401,21 @@ int attention_tc_f32(Ctx* ctx, const AttnProblem& p, const void* Q, const void* 
     kp.causal_off = int(p.Skv - p.Sq);
     kp.scale_log2 = p.scale * 1.4426950408889634f;
     kp.O = O; kp.os_b = p.os[0]; kp.os_h = p.os[1]; kp.os_s = p.os[2];
+    kp.O_hi = nullptr; kp.O_lo = nullptr;
     kp.status = ctx->status_dev;
     static const bool persistent = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT"); return !e || e[0] != '0'; }();
     static const bool persistent_causal = [] { const char* e = getenv("DOCC_B200_ATTENTION_PERSISTENT_CAUSAL"); return !e || e[0] != '0'; }();
-    if (persistent && (!p.causal || (persistent_causal && p.Skv >= p.Sq)) && p.Sq > kBQ) return launch2p<64, true, true>(ctx, p, maps, kp, 4);
+    if (persistent && (!p.causal || (persistent_causal && p.Skv >= p.Sq)) && p.Sq > kBQ) {
+        // the caller's operand planes for what consumes O (16-byte stores: strides and bases as for the fp32 output)
+        const bool planes = p.o_hi && p.o_lo && p.planes_done && reinterpret_cast<uintptr_t>(p.o_hi) % 16 == 0 &&
+                            reinterpret_cast<uintptr_t>(p.o_lo) % 16 == 0 && p.os[0] % 8 == 0 && p.os[1] % 8 == 0 && p.os[2] % 8 == 0;
+        if (planes) {
+            kp.O_hi = p.o_hi;
+            kp.O_lo = p.o_lo;
+            *p.planes_done = true;
+        }
+        return launch2p<64, true, true>(ctx, p, maps, kp, 4);
+    }
     return launch2<64, true, true>(ctx, p, maps, kp, 4);
 }
 

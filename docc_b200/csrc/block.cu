@@ -68,8 +68,19 @@ int block_device(Ctx* ctx, int prec, const docc_b200_block_params& p, const void
     a.qs[0] = a.ks[0] = a.vs[0] = p.seq * 3 * d; a.qs[1] = a.ks[1] = a.vs[1] = dh; a.qs[2] = a.ks[2] = a.vs[2] = 3 * d;
     a.os[0] = p.seq * d; a.os[1] = dh; a.os[2] = d;
     const char* q = static_cast<const char*>(qkv);
+    // fp32: the attention kernel may write its output as the out-projection's operand planes (same workspace slot and
+    // layout as above: [T][d], lo behind hi); `att` then stays unwritten and the out-projection skips its split pass
+    bool att_planes = false;
+    if (prec == DOCC_B200_PREC_S && d % 8 == 0) {
+        void* planes;
+        DOCC_TRY(get_workspace(ctx, 0, size_t(T) * size_t(d) * 2 * sizeof(__nv_bfloat16), &planes));
+        a.o_hi = planes;
+        a.o_lo = static_cast<__nv_bfloat16*>(planes) + size_t(T) * size_t(d);
+        a.planes_done = &att_planes;
+    }
     DOCC_TRY(attention_device(ctx, a, q, q + size_t(d) * es, q + size_t(2 * d) * es, att, 0));
-    DOCC_TRY(linear_device(ctx, prec, T, d, d, att, d, p.w_o, d, static_cast<const float*>(p.b_o), DOCC_B200_ACT_NONE, X, d, h, d));
+    DOCC_TRY(linear_device(ctx, prec, T, d, d, att, d, p.w_o, d, static_cast<const float*>(p.b_o), DOCC_B200_ACT_NONE, X, d, h, d,
+                           att_planes));
     DOCC_TRY(ln_into_planes(h, p.ln2_g, p.ln2_b, &fused));
     if (!fused) DOCC_TRY(layernorm_any(ctx, prec, T, d, h, p.ln2_g, p.ln2_b, p.eps, h2));
     DOCC_TRY(linear_device(ctx, prec, T, dff, d, h2, d, p.w_1, d, static_cast<const float*>(p.b_1), DOCC_B200_ACT_GELU_ERF, nullptr,
