@@ -57,6 +57,19 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
+// packed pairs of fp32 (sm_100): (y0, y1) = (x0, x1) * a + c, and (a0, a1) += (x0, x1), one instruction each
+__device__ __forceinline__ void fma2(float& y0, float& y1, float x0, float x1, float a, float c) {
+    asm("{\n.reg .b64 s, sa, sc, r;\nmov.b64 s, {%2, %3};\nmov.b64 sa, {%4, %4};\nmov.b64 sc, {%5, %5};\nfma.rn.f32x2 r, s, sa, sc;\n"
+        "mov.b64 {%0, %1}, r;\n}"
+        : "=f"(y0), "=f"(y1)
+        : "f"(x0), "f"(x1), "f"(a), "f"(c));
+}
+__device__ __forceinline__ void add2(float& a0, float& a1, float x0, float x1) {
+    asm("{\n.reg .b64 s, t, r;\nmov.b64 s, {%0, %1};\nmov.b64 t, {%2, %3};\nadd.rn.f32x2 r, s, t;\nmov.b64 {%0, %1}, r;\n}"
+        : "+f"(a0), "+f"(a1)
+        : "f"(x0), "f"(x1));
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float r;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -660,13 +673,17 @@ __global__ void __launch_bounds__(320, 1)
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    float x0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_ref));
-                    float x1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref));
+                    // two scores per instruction for the scaling and for the row sum (packed fp32 pairs, sm_100): the softmax
+                    // warps are bound by instruction issue, not by the exponential unit
+                    float a0, a1;
+                    fma2(a0, a1, __uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref);
+                    float x0 = ex2(a0);
+                    float x1 = ex2(a1);
                     if (MASK) {
                         if (c * 32 + 2 * i > visible) x0 = 0.f;
                         if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
                     }
-                    bl4[i & 3] += x0 + x1;
+                    add2(bl4[(i & 1) * 2], bl4[(i & 1) * 2 + 1], x0, x1);
                     pk[i] = pack2<IS_BF16>(x0, x1);
                     if (SPLIT) {
                         const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
@@ -1098,13 +1115,17 @@ __global__ void __launch_bounds__(320, 1)
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    float x0 = ex2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_ref));
-                    float x1 = ex2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref));
+                    // two scores per instruction for the scaling and for the row sum (packed fp32 pairs, sm_100): the softmax
+                    // warps are bound by instruction issue, not by the exponential unit
+                    float a0, a1;
+                    fma2(a0, a1, __uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_ref);
+                    float x0 = ex2(a0);
+                    float x1 = ex2(a1);
                     if (MASK) {
                         if (c * 32 + 2 * i > visible) x0 = 0.f;
                         if (c * 32 + 2 * i + 1 > visible) x1 = 0.f;
                     }
-                    bl4[i & 3] += x0 + x1;
+                    add2(bl4[(i & 1) * 2], bl4[(i & 1) * 2 + 1], x0, x1);
                     pk[i] = pack2<IS_BF16>(x0, x1);
                     if (SPLIT) {
                         const float h0 = __uint_as_float(pk[i] << 16), h1 = __uint_as_float(pk[i] & 0xffff0000u);
