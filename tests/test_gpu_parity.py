@@ -531,6 +531,22 @@ def test_transformer_block_fp32(rt):
     assert relerr(got_h, ref) <= TOL_F32
 
 
+@pytest.mark.parametrize("batch,seq", [(40, 128), (12, 448)])
+def test_transformer_block_fp32_fused_operand_planes(rt, batch, seq):
+    # Enough rows (>= 2 * 16 * SMs) for the LayerNorms to write the next GEMM's bf16 hi / lo planes themselves. With one query
+    # tile per head (seq 128) the attention kernel writes plain fp32 and the out-projection splits as usual; with several
+    # (seq 448) the persistent kernel writes the out-projection's planes too. Second opinion as for the config-5 tests: the
+    # fp64 composition on the device (the oracle's loops would take minutes at these row counts).
+    d, heads, dff = 256, 4, 512
+    torch.manual_seed(batch)
+    p = make_block_nontrivial(d, dff)
+    x = torch.randn(batch, seq, d)
+    got = host(ops.transformer_block(x.cuda(), {k: v.cuda() for k, v in p.items()}, heads))
+    assert relerr(got, torch_block_f64(x, p, heads)) <= TOL_F32
+    sub = oracle.transformer_block(x[:1].numpy(), {k: v.numpy() for k, v in p.items()}, heads)  # one sequence through the oracle
+    assert relerr(got[:1], sub) <= TOL_F32
+
+
 def test_transformer_block_bf16(rt):
     d, heads, dff = 256, 4, 512
     p = make_block(d, dff)
