@@ -1335,6 +1335,13 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     // resident weights: 3x3 filter, one channel block, one tile of output channels, weights read where they lie
     static const int wres_mode = [] { const char* e = getenv("DOCC_B200_CONV_WRES"); return e ? atoi(e) : 1; }();
     const bool wres = wres_mode && q.C == 64 && q.c_out <= 128 && q.kh == 3 && q.kw == 3 && reinterpret_cast<uintptr_t>(Wt) % 16 == 0;
+    if (wres) {
+        // two-row accumulators: a tile's height is not tied to one accumulator's 256 columns any more, only to the halo
+        // slots' share of shared memory. Six rows (eight halo rows per slot, a six-chunk input ring) measured best on
+        // [32,64,56,56]: 22.6 us at four rows, 21.7 at six, 24.3 at eight (the input ring shrinks to two chunks)
+        static const int wres_rmax = [] { const char* e = getenv("DOCC_B200_CONV_WRES_RMAX"); return e ? atoi(e) : 6; }();
+        if (wres_rmax >= 2 && wres_rmax <= 8) p.r_max = wres_rmax;
+    }
     void* ww = nullptr;
     if (!wres) DOCC_TRY(get_workspace(ctx, 1, w_elems * 2 + 256, &ww));  // the re-laid copy of the streamed form
     __nv_bfloat16* w_hi = static_cast<__nv_bfloat16*>(ww);
