@@ -692,7 +692,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     auto tempty_bar = [&](uint32_t i) { return bars + 176u + 8u * i; };
     auto full_x = [&](uint32_t i) { return bars + 192u + 8u * i; };
     auto empty_x = [&](uint32_t i) { return bars + 256u + 8u * i; };
-    const uint32_t wres_bar = bars + 120u;  // WRES: taps 0-7 are in tensor memory (one arrival per loading warp)
+    // WRES: channels 16k..16k+15 of every tap are where the tensor core reads them (one arrival per loading warp); the
+    // last of the four is also the sign that all weights are in place
+    auto wres_k = [&](uint32_t k) { return bars + 96u + 8u * k; };
+    const uint32_t wres_bar = wres_k(3);
+    const uint32_t first_rows_bar = bars + 88u;  // WRES: the first tile's halo rows 0-3 are assembled (what its first two output rows read)
     // WRES start-up ring: the epilogue's staging tiles (two blocks of 16 KB, unused until the first accumulator is full)
     // and as much of halo slot 1 as holds whole blocks (unused until the second tile is assembled; the transposers wait
     // for wres_bar before they write there)
@@ -709,7 +713,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                 mbar_init(full_a(i), 1);
                 mbar_init(empty_a(i), 4);
             }
-            mbar_init(wres_bar, 4);
+            for (uint32_t k = 0; k < 4; k++) mbar_init(wres_k(k), 4);
+            mbar_init(first_rows_bar, 4);
         } else {
             for (uint32_t i = 0; i < w_stages; i++) {
                 mbar_init(full_a(i), 1);
@@ -725,6 +730,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         fence_barrier_init();
         prefetch_tensormap(&tmW0);
         prefetch_tensormap(&tmY);
+        if constexpr (WRES) {
+            // the first pieces of the weights go out before the block-wide synchronisation (the stages are free)
+            griddep_wait();
+            for (uint32_t st = 0; st < res_stages; st++) {
+                mbar_arrive_expect_tx(full_a(st), kResPieceBytes);
+                tma_load_2d(res_stage_addr(st), &tmW0, full_a(st), int(st) * 72, 0);
+            }
+        }
     }
     const long long u_begin = p.total_units * blockIdx.x / gridDim.x;
     const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
@@ -773,8 +786,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         // weight producer: kh*kw blocks of 128 x 64 per (tile, channel block)
         if (WRES && lane == 0) {
             // once: the eight 144-byte pieces of every output channel's row through the borrowed stages
-            uint32_t st = 0, use = 0;
-            for (uint32_t piece = 0; piece < 8; piece++) {
+            uint32_t st = 0, use = 1;
+            for (uint32_t piece = res_stages; piece < 8; piece++) {
                 if (!mbar_wait(empty_a(st), (use & 1u) ^ 1u)) {
                     conv_timeout(p.status, 31);
                     break;
@@ -862,20 +875,44 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             uint32_t s = 0, ph = 0, hs = 0, hph = 0;
             uint64_t a_desc = a_desc0;
             if constexpr (WRES) {
-                if (!mbar_wait(wres_bar, 0)) {
-                    conv_timeout(p.status, 39);
-                    ok = false;
-                }
-                tc_fence_after();
                 uint32_t abuf = 0, aph = 0;
+                bool first = true;
                 while (ok && next_tile(p, u, u_end, t)) {
-                    if (!mbar_wait(full_h(hs), hph)) {
+                    if (!mbar_wait(first ? first_rows_bar : full_h(hs), first ? 0u : hph)) {
                         conv_timeout(p.status, 36);
                         break;
                     }
                     tc_fence_after();
                     const uint64_t slot_desc = h_desc0 + uint64_t(hs * (halo_bytes >> 4));
-                    for (int rr = 0; rr < t.rows && ok; rr += 2) {
+                    if (first) {
+                        // The first two output rows chase the weights: 16 channels of all nine taps at a time, as the
+                        // loading warps hand them over. (Their accumulator is free: nothing has used it.)
+                        const uint32_t idesc = make_idesc(128, t.rows >= 2 ? 128 : 64, 1, 0, 0);
+                        const uint32_t d_tmem = tmem_base + kResAccCol;
+                        for (uint32_t k = 0; k < 4 && ok; k++) {
+                            if (!mbar_wait(wres_k(k), 0)) {
+                                conv_timeout(p.status, 39);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+#pragma unroll
+                            for (int tap = 0; tap < int(kResTmemTaps); tap++)
+                                umma_f16_ts(d_tmem, tmem_base + uint32_t(tap) * 32u + k * 8u,
+                                            slot_desc + uint64_t(((tap / 3) * 64 + tap % 3) * 8) + uint64_t(k * 2u), idesc, (k | uint32_t(tap)) ? 1u : 0u);
+                            umma_f16_ss(d_tmem, a_desc0 + uint64_t(k * 2u), slot_desc + uint64_t((2 * 64 + 2) * 8) + uint64_t(k * 2u), idesc, 1u);
+                        }
+                        if (!ok) break;
+                        umma_commit(tfull_bar(0));
+                        abuf = 1;
+                        // the rest of the tile reads all of its halo rows
+                        if (!mbar_wait(full_h(hs), hph)) {
+                            conv_timeout(p.status, 36);
+                            break;
+                        }
+                        tc_fence_after();
+                    }
+                    for (int rr = first ? 2 : 0; rr < t.rows && ok; rr += 2) {
                         if (!mbar_wait(tempty_bar(abuf), aph ^ 1u)) {
                             conv_timeout(p.status, 32);
                             ok = false;
@@ -898,6 +935,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                         }
                     }
                     if (!ok) break;
+                    first = false;
                     umma_commit(empty_h(hs));
                     if (++hs == uint32_t(kHaloSlots)) {
                         hs = 0;
@@ -964,7 +1002,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         long long u = u_begin;
         Tile t;
         bool ok = true;
-        bool wres_seen = false;
+        bool wres_seen = false, first_tile = true;
         while (ok && next_tile(p, u, u_end, t)) {
             const int hrows = t.rows + p.kh - 1;
             for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
@@ -1022,6 +1060,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_x(xs));  // this warp has read its part of the chunk
+                    if constexpr (WRES) {
+                        if (first_tile && hr == (hrows > 4 ? 3 : hrows - 1)) {  // what the first two output rows read is in place
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(first_rows_bar);
+                        }
+                    }
                     if (++xs == n_chunks) {
                         xs = 0;
                         xph ^= 1u;
@@ -1031,6 +1076,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                 fence_proxy_async_smem();  // the tensor core reads these generic-proxy stores through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_h(hs));
+                first_tile = false;
                 if (++hs == uint32_t(kHaloSlots)) {
                     hs = 0;
                     hph ^= 1u;
@@ -1099,12 +1145,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                         st = 0;
                         use++;
                     }
+                    if (piece & 1u) {  // 16 channels of every tap are complete: the tensor core may use them
+                        tmem_st_wait();
+                        fence_proxy_async_smem();  // tap 8's block was written with generic stores; the tensor core reads it through the async proxy
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(wres_k(piece >> 1));
+                    }
                 }
-                tmem_st_wait();
-                fence_proxy_async_smem();  // tap 8's block was written with generic stores; the tensor core reads it through the async proxy
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0 && wok) mbar_arrive(wres_bar);
             }
         }
         uint32_t abuf = 0, aph = 0;  // WRES: accumulator of the current pair of output rows
