@@ -68,6 +68,25 @@ struct Tile {
 // [i*U/G, (i+1)*U/G) and cuts it into tiles of at most r_max rows inside one image.
 __device__ __forceinline__ bool next_tile(const ConvKernelParams& p, long long& u, long long u_end, Tile& t) {
     if (u >= u_end) return false;
+    if (p.total_units <= 0x7fffffffLL) {
+        // the usual case in 32-bit arithmetic: the 64-bit divisions below cost the one thread that issues the tensor-core
+        // work about a thousand clocks between two tiles
+        const uint32_t u32 = uint32_t(u), rows_total = uint32_t(p.N) * uint32_t(p.Ho);
+        const uint32_t mt = u32 / rows_total, row = u32 - mt * rows_total;
+        const uint32_t n = row / uint32_t(p.Ho), oh0 = row - n * uint32_t(p.Ho);
+        t.m0 = int(mt) * 128;
+        t.n = int(n);
+        t.oh0 = int(oh0);
+        uint32_t rem = uint32_t(p.Ho) - oh0;
+        if (rem > uint32_t(u_end - u)) rem = uint32_t(u_end - u);
+        const uint32_t rmax = uint32_t(p.r_max);
+        const uint32_t nt = (rem + rmax - 1) / rmax;
+        uint32_t r = (rem + nt - 1) / nt;
+        if (p.even_rows && (r & 1u) && r < rem && r < rmax) r++;
+        t.rows = int(r);
+        u += r;
+        return true;
+    }
     const long long rows_total = (long long)p.N * p.Ho;
     const long long mt = u / rows_total;
     const long long row = u - mt * rows_total;
@@ -626,6 +645,7 @@ __device__ __forceinline__ void weight_relayout(const TIn* __restrict__ Wt, __nv
 // channels out of their 144 bytes with byte permutes and store them as four tensor-memory columns (taps 0-7) or as
 // one 16-byte chunk of the shared-memory block in the UMMA's swizzled K-major layout (tap 8).
 constexpr int kFusedThreads = 480;
+constexpr uint32_t kTileList = 8;  // tiles of a CTA worked out once, ahead of the roles that walk them
 constexpr uint32_t kResAccCol = 256;  // first accumulator column of the resident-weights variant
 constexpr uint32_t kResTmemTaps = 8;  // taps held in tensor memory; the ninth stays in shared memory
 constexpr uint32_t kResPieceBytes = 128 * 144;  // one start-up piece: eight channels x nine taps of 128 output channels
@@ -696,7 +716,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     // last of the four is also the sign that all weights are in place
     auto wres_k = [&](uint32_t k) { return bars + 96u + 8u * k; };
     const uint32_t wres_bar = wres_k(3);
-    const uint32_t first_rows_bar = bars + 88u;  // WRES: the first tile's halo rows 0-3 are assembled (what its first two output rows read)
+    // WRES: a slot's halo rows 0-3 are assembled (what the tile's first two output rows read; one arrival per transposer warp)
+    auto part_h = [&](uint32_t i) { return bars + 32u + 8u * i; };
     // WRES start-up ring: the epilogue's staging tiles (two blocks of 16 KB, unused until the first accumulator is full)
     // and as much of halo slot 1 as holds whole blocks (unused until the second tile is assembled; the transposers wait
     // for wres_bar before they write there)
@@ -714,7 +735,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                 mbar_init(empty_a(i), 4);
             }
             for (uint32_t k = 0; k < 4; k++) mbar_init(wres_k(k), 4);
-            mbar_init(first_rows_bar, 4);
+            for (uint32_t i = 0; i < 2; i++) mbar_init(part_h(i), 4);
         } else {
             for (uint32_t i = 0; i < w_stages; i++) {
                 mbar_init(full_a(i), 1);
@@ -743,6 +764,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     const long long u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
     const int cblocks = p.C / 64;
     const int x0 = p.pad_w > 0 ? -8 : 0;  // first input column of a staging chunk
+    // The CTA's first tiles, worked out once by a thread with nothing else to do before the synchronisation. Cutting the
+    // range into tiles takes integer divisions, several hundred clocks on one thread, which the roles below would each
+    // spend between two tiles: the thread that issues the tensor-core work on the critical path.
+    const uint32_t tile_list = bars + 400u;
+    volatile uint32_t* list_count = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 384u - raw_addr));
+    volatile long long* list_after = reinterpret_cast<volatile long long*>(smem_raw + (bars + 392u - raw_addr));
+    if (warp == 2 && lane == 0) {
+        long long u = u_begin;
+        Tile t;
+        uint32_t n = 0;
+        while (n < kTileList && next_tile(p, u, u_end, t)) {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile_list + 16u * n), "r"(t.m0), "r"(t.n), "r"(t.oh0), "r"(t.rows) : "memory");
+            n++;
+        }
+        *list_count = n;
+        *list_after = u;
+    }
     // The input producer owns the barriers of its ring and fills the ring before the block-wide synchronisation: the
     // first rows (a trip to HBM) are then in flight while tensor memory is allocated and the other barriers are set up.
     uint32_t x_early = 0;
@@ -775,6 +813,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    const uint32_t n_list = *list_count;
+    const long long u_after = *list_after;
+    // tile number i of this CTA: from the list while it lasts, then cut from the rest of the range (cursor u)
+    auto tile_at = [&](uint32_t& i, long long& u, Tile& t) -> bool {
+        if (i < n_list) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(t.m0), "=r"(t.n), "=r"(t.oh0), "=r"(t.rows) : "r"(tile_list + 16u * i) : "memory");
+            i++;
+            return true;
+        }
+        return next_tile(p, u, u_end, t);
+    };
     if constexpr (WRES) {
         // barrier set-up, tensor-memory allocation and descriptor prefetch above overlap the tail of the launch before;
         // the launch after this one may begin its own set-up as soon as SMs free up
@@ -877,8 +926,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
             if constexpr (WRES) {
                 uint32_t abuf = 0, aph = 0;
                 bool first = true;
-                while (ok && next_tile(p, u, u_end, t)) {
-                    if (!mbar_wait(first ? first_rows_bar : full_h(hs), first ? 0u : hph)) {
+                uint32_t li = 0;
+                long long ul = u_after;
+                while (ok && tile_at(li, ul, t)) {
+                    // a tile's first two output rows start as soon as the four halo rows they read are there
+                    if (!mbar_wait(part_h(hs), hph)) {
                         conv_timeout(p.status, 36);
                         break;
                     }
@@ -905,14 +957,16 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                         if (!ok) break;
                         umma_commit(tfull_bar(0));
                         abuf = 1;
-                        // the rest of the tile reads all of its halo rows
-                        if (!mbar_wait(full_h(hs), hph)) {
-                            conv_timeout(p.status, 36);
-                            break;
-                        }
-                        tc_fence_after();
                     }
                     for (int rr = first ? 2 : 0; rr < t.rows && ok; rr += 2) {
+                        if (rr == 2) {  // the rest of the tile reads all of its halo rows
+                            if (!mbar_wait(full_h(hs), hph)) {
+                                conv_timeout(p.status, 36);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                        }
                         if (!mbar_wait(tempty_bar(abuf), aph ^ 1u)) {
                             conv_timeout(p.status, 32);
                             ok = false;
@@ -999,11 +1053,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         const int m = lane >> 3, r = lane & 7;  // this lane supplies row r of 8x8 block m to ldmatrix / stmatrix
         const int shift = p.pad_w + x0;         // slot = staging pixel + shift (<= 0)
         uint32_t xs = 0, xph = 0, hs = 0, hph = 0;
-        long long u = u_begin;
+        long long u = u_after;
+        uint32_t li = 0;
         Tile t;
         bool ok = true;
-        bool wres_seen = false, first_tile = true;
-        while (ok && next_tile(p, u, u_end, t)) {
+        bool wres_seen = false;
+        while (ok && tile_at(li, u, t)) {
             const int hrows = t.rows + p.kh - 1;
             for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
                 if (!mbar_wait(empty_h(hs), hph ^ 1u)) {
@@ -1061,10 +1116,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(empty_x(xs));  // this warp has read its part of the chunk
                     if constexpr (WRES) {
-                        if (first_tile && hr == (hrows > 4 ? 3 : hrows - 1)) {  // what the first two output rows read is in place
+                        if (hr == (hrows > 4 ? 3 : hrows - 1)) {  // what the tile's first two output rows read is in place
                             fence_proxy_async_smem();
                             __syncwarp();
-                            if (lane == 0) mbar_arrive(first_rows_bar);
+                            if (lane == 0) mbar_arrive(part_h(hs));
                         }
                     }
                     if (++xs == n_chunks) {
@@ -1076,7 +1131,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
                 fence_proxy_async_smem();  // the tensor core reads these generic-proxy stores through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_h(hs));
-                first_tile = false;
                 if (++hs == uint32_t(kHaloSlots)) {
                     hs = 0;
                     hph ^= 1u;
@@ -1157,7 +1211,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
         }
         uint32_t abuf = 0, aph = 0;  // WRES: accumulator of the current pair of output rows
         bool alive = true;
-        while (alive && next_tile(p, u, u_end, t)) {
+        uint32_t li = 0;
+        u = u_after;
+        while (alive && tile_at(li, u, t)) {
             const uint32_t buf = lt & 1u, use = lt >> 1;
             lt++;
             if constexpr (!WRES) {
@@ -1420,7 +1476,7 @@ int launch_fused(Ctx* ctx, const ConvTcProblem& q, ConvKernelParams p, const voi
     }
     // shared memory: two halo slots, eight epilogue staging tiles, then the two rings share what is left
     const size_t halo_total = size_t(kHaloSlots) * size_t(p.r_max + p.kh - 1) * 8192;
-    const size_t fixed = 8 * 4096 + 512 + 1024 + 512;
+    const size_t fixed = 8 * 4096 + 512 + 1024 + 512 + 128;  // staging tiles, dummy rows, barriers and the tile list, alignment slack
     const size_t rings = 227 * 1024 - halo_total - fixed;
     static const int x_chunks_env = [] { const char* e = getenv("DOCC_B200_CONV_XCHUNKS"); return e ? atoi(e) : 0; }();
     int x_chunks = x_chunks_env >= 2 && x_chunks_env <= 8 ? x_chunks_env : 4;
