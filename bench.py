@@ -211,7 +211,7 @@ def make_workload(name, torch, ops, rank, world, strong=False):
 
         return dict(step=step, units=2 * 1000 ** 3, unit="TFLOP/s", scale=1e-12, metric="gemm_fp64_tflops", dtype="f64",
                     bound="tensor", peak=FP64_TFLOPS_BUILDER_MEASURED, peak_source="of the builder-measured cuBLAS DGEMM 8192^3 rate",
-                    launches_per_step=1, steps_scale=5,
+                    launches_per_step=1, steps_scale=20,
                     config={"workload": WORKLOAD_TEXT["gemm_f64"], "l2": "operands and results rotated over 8 sets, larger than L2"},
                     kind="gemm", replicas_only=True)
 
@@ -306,7 +306,8 @@ def make_workload(name, torch, ops, rank, world, strong=False):
 
         return dict(step=step, config={"workload": wtext, "batch_per_gpu": n_local,
                                        "l2": "inputs and outputs rotated over 6 buffer sets, larger than L2"},
-                    steps_scale=5, **common)  # 30-70 us steps: five times the steps of the other extras cost nothing
+                    steps_scale=20, **common)  # 20-60 us steps: twenty times the steps of the other extras cost nothing and
+        # keep the first launch's latency and the host's jitter out of the per-step figure
 
     if name in ("attention", "attention_causal"):
         causal = name.endswith("causal")

@@ -339,6 +339,8 @@ def test_conv_tensor_core_geometries(rt, n, c, h, w, co, k, pad):
     (2, 64, 14, 40, 48, 5, 2),    # 5x5 filter
     (1, 64, 12, 24, 64, 7, 3),    # 7x7 filter: shallow rings
     (1, 64, 30, 56, 128, 3, 1),
+    (8, 64, 1000, 16, 32, 3, 1),  # tall images: more tiles per CTA than its precomputed tile list holds (resident weights)
+    (4, 128, 1000, 16, 32, 3, 1), # the same with streamed weights (two channel blocks)
 ])
 def test_conv_16bit_nchw_in_place(rt, dtype, n, c, h, w, co, k, pad):
     torch.manual_seed(11)
