@@ -47,6 +47,7 @@ struct ConvKernelParams {
     int x_chunks;  // fused variant: depth of the input staging ring
     int tma_out;  // Y rows are 16-byte aligned: full 32-pixel groups go out through TMA stores
     int even_rows;  // tiles of an even number of rows where the range allows it (two-row accumulators)
+    int paired;  // halo variant, split operands: three halo slots, the high weight plane streamed once for both input planes
     const float* bias;
     float* Y;
     DeviceStatus* status;
@@ -353,14 +354,15 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     const uint32_t halo_bytes = uint32_t(p.r_max + p.kh - 1) * 8192u;
     const uint32_t w_stages = uint32_t(p.w_stages);
+    const uint32_t n_slots = p.paired == 1 ? 3u : uint32_t(kHaloSlots);
     const uint32_t sH = base;                           // halo slots; reads past a slot's end land in the next region
-    const uint32_t sA = sH + kHaloSlots * halo_bytes;   // weight ring
+    const uint32_t sA = sH + n_slots * halo_bytes;      // weight ring
     const uint32_t sStage = sA + w_stages * kABytes;    // eight 4 KB staging tiles (one per epilogue warp)
     const uint32_t bars = sStage + 8 * 4096u;
     auto full_a = [&](uint32_t i) { return bars + 8u * i; };
     auto empty_a = [&](uint32_t i) { return bars + 64u + 8u * i; };
-    auto full_h = [&](uint32_t i) { return bars + 128u + 8u * i; };
-    auto empty_h = [&](uint32_t i) { return bars + 144u + 8u * i; };
+    auto full_h = [&](uint32_t i) { return bars + 128u + 8u * i; };   // up to three halo slots
+    auto empty_h = [&](uint32_t i) { return bars + 200u + 8u * i; };
     auto tfull_bar = [&](uint32_t i) { return bars + 160u + 8u * i; };
     auto tempty_bar = [&](uint32_t i) { return bars + 176u + 8u * i; };
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_raw + (bars + 192u - raw_addr));
@@ -372,9 +374,11 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             mbar_init(full_a(i), 1);
             mbar_init(empty_a(i), 1);
         }
-        for (uint32_t i = 0; i < 2; i++) {
+        for (uint32_t i = 0; i < 3; i++) {
             mbar_init(full_h(i), 1);
             mbar_init(empty_h(i), 1);
+        }
+        for (uint32_t i = 0; i < 2; i++) {
             mbar_init(tfull_bar(i), 1);
             mbar_init(tempty_bar(i), 8);
         }
@@ -404,6 +408,42 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
             long long u = u_begin;
             Tile t;
             bool ok = true;
+            while (ok && p.paired && next_tile(p, u, u_end, t)) {
+                // Split operands, paired form: per channel block the high and the low plane of the input go into two
+                // slots; the low weight plane runs over the high input, then every block of the high weight plane is
+                // used for both input planes (18 weight blocks and two halo boxes per tile and channel block, not 27 and 3).
+                for (int c0 = 0; c0 < p.C && ok; c0 += 64) {
+                    for (int pl = 0; pl < 2 && ok; pl++) {
+                        if (!mbar_wait(empty_h(hs), hph ^ 1u)) {
+                            conv_timeout(p.status, 25);
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(full_h(hs), halo_bytes);
+                        tma_load_4d(sH + hs * halo_bytes, pl ? &tmX1 : &tmX0, full_h(hs), c0, -p.pad_w, t.oh0 - p.pad_h, t.n);
+                        if (++hs == n_slots) {
+                            hs = 0;
+                            hph ^= 1u;
+                        }
+                    }
+                    for (int wp = 1; wp >= 0 && ok; wp--) {  // low weight plane first (small terms first)
+                        int k_col = c0;
+                        for (int tap = 0; tap < p.kh * p.kw; tap++, k_col += p.C) {
+                            if (!mbar_wait(empty_a(s), ph ^ 1u)) {
+                                conv_timeout(p.status, 21);
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_expect_tx(full_a(s), kABytes);
+                            tma_load_2d(sA + s * kABytes, wp ? &tmW1 : &tmW0, full_a(s), k_col, t.m0);
+                            if (++s == w_stages) {
+                                s = 0;
+                                ph ^= 1u;
+                            }
+                        }
+                    }
+                }
+            }
             while (ok && next_tile(p, u, u_end, t)) {
                 for (int pass = 0; pass < p.npass && ok; pass++) {
                     const CUtensorMap* mw = p.pw[pass] ? &tmW1 : &tmW0;
@@ -416,7 +456,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                         }
                         mbar_arrive_expect_tx(full_h(hs), halo_bytes);
                         tma_load_4d(sH + hs * halo_bytes, mx, full_h(hs), c0, -p.pad_w, t.oh0 - p.pad_h, t.n);
-                        if (++hs == uint32_t(kHaloSlots)) {
+                        if (++hs == n_slots) {
                             hs = 0;
                             hph ^= 1u;
                         }
@@ -465,7 +505,55 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                 const uint32_t idesc = make_idesc(128, t.rows * 64, 1, 0, 0);
                 const uint32_t d_tmem = tmem_base + buf * 256u;
                 uint32_t acc = 0;
-                for (int cb = 0; cb < cblocks && ok; cb++) {
+                for (int cb = 0; p.paired && cb < p.C / 64 && ok; cb++) {
+                    // slots: hs holds the high plane of the input, the one after it the low plane
+                    const uint32_t hs_lo = hs + 1u == n_slots ? 0u : hs + 1u;
+                    const uint32_t hph_lo = hs + 1u == n_slots ? hph ^ 1u : hph;
+                    for (int wp = 1; wp >= 0 && ok; wp--) {
+                        if (!mbar_wait(wp ? full_h(hs) : full_h(hs_lo), wp ? hph : hph_lo)) {
+                            conv_timeout(p.status, 26);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        uint64_t row_hi = h_desc0 + uint64_t(hs * (halo_bytes >> 4)), row_lo = h_desc0 + uint64_t(hs_lo * (halo_bytes >> 4));
+                        for (int ky = 0; ky < p.kh && ok; ky++, row_hi += (64 * 128) >> 4, row_lo += (64 * 128) >> 4) {
+                            uint64_t b_hi = row_hi, b_lo = row_lo;
+                            for (int kx = 0; kx < p.kw; kx++, b_hi += 128 >> 4, b_lo += 128 >> 4) {
+                                if (!mbar_wait(full_a(s), ph)) {
+                                    conv_timeout(p.status, 23);
+                                    ok = false;
+                                    break;
+                                }
+                                tc_fence_after();
+                                if (wp) {
+                                    umma_f16_ss_x4<1>(d_tmem, a_desc, b_hi, idesc, acc, 2, 2);  // W_lo * X_hi
+                                } else {
+                                    umma_f16_ss_x4<1>(d_tmem, a_desc, b_lo, idesc, 1u, 2, 2);   // W_hi * X_lo
+                                    umma_f16_ss_x4<1>(d_tmem, a_desc, b_hi, idesc, 1u, 2, 2);   // W_hi * X_hi
+                                }
+                                acc = 1;
+                                umma_commit(empty_a(s));
+                                a_desc += kABytes >> 4;
+                                if (++s == w_stages) {
+                                    s = 0;
+                                    ph ^= 1u;
+                                    a_desc = a_desc0;
+                                }
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(empty_h(hs));
+                    umma_commit(empty_h(hs_lo));
+                    for (int i = 0; i < 2; i++) {
+                        if (++hs == n_slots) {
+                            hs = 0;
+                            hph ^= 1u;
+                        }
+                    }
+                }
+                for (int cb = 0; !p.paired && cb < cblocks && ok; cb++) {
                     if (!mbar_wait(full_h(hs), hph)) {
                         conv_timeout(p.status, 26);
                         ok = false;
@@ -495,7 +583,7 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                     }
                     if (!ok) break;
                     umma_commit(empty_h(hs));
-                    if (++hs == uint32_t(kHaloSlots)) {
+                    if (++hs == n_slots) {
                         hs = 0;
                         hph ^= 1u;
                     }
@@ -1641,8 +1729,13 @@ int conv_tc(Ctx* ctx, const ConvTcProblem& q, const void* X, const void* Wt, con
     p.bias = bias; p.Y = Y; p.status = ctx->status_dev;
 
     if (halo) {
-        const size_t halo_total = size_t(kHaloSlots) * size_t(p.r_max + p.kh - 1) * 8192;
         const size_t fixed = 8 * 4096 + 1024 + 256;
+        const size_t slot_bytes = size_t(p.r_max + p.kh - 1) * 8192;
+        // split operands: a third halo slot (both input planes of a tile resident, the next tile's first plane in flight)
+        // when it leaves a weight ring of three stages
+        static const int paired_mode = [] { const char* e = getenv("DOCC_B200_CONV_PAIRED"); return e ? atoi(e) : 1; }();
+        p.paired = (split && paired_mode == 1 && 227 * 1024 >= 3 * slot_bytes + fixed + 3 * kABytes) ? 1 : (split && paired_mode == 2) ? 2 : 0;
+        const size_t halo_total = size_t(p.paired == 1 ? 3 : kHaloSlots) * slot_bytes;
         int w_stages = int((227 * 1024 - halo_total - fixed) / kABytes);
         if (w_stages > kMaxWStages) w_stages = kMaxWStages;
         p.w_stages = w_stages;
