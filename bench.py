@@ -36,7 +36,7 @@ from docc_b200.sharding import GatherPlan  # noqa: E402
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's dominant kernel, from the ncu captures
 # (isolated launches: part of the write-back is still in L2 when the kernel ends, which is why the softmax figure is
 # below its 268 MB of algorithmic bytes)
-NCU_TRAFFIC_BYTES = {"softmax": 213.9e6, "gemm_bf16": 1001.2e6, "conv_bf16": 14.9e6, "conv_f32": 33.5e6, "attention": 243.7e6, "attention_causal": 566.4e6,
+NCU_TRAFFIC_BYTES = {"softmax": 213.9e6, "gemm_bf16": 1001.2e6, "conv_bf16": 14.9e6, "conv_f32": 28.6e6, "attention": 243.7e6, "attention_causal": 566.4e6,
                      "gemm_f64": 16.0e6}
 
 # Sharded workloads (conv, attention, encoder block) at N > 1 GPUs are read two ways. Weak (the headline `value`): every
