@@ -426,9 +426,9 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                             hph ^= 1u;
                         }
                     }
-                    for (int wp = 1; wp >= 0 && ok; wp--) {  // low weight plane first (small terms first)
-                        int k_col = c0;
-                        for (int tap = 0; tap < p.kh * p.kw; tap++, k_col += p.C) {
+                    int k_col = c0;
+                    for (int tap = 0; tap < p.kh * p.kw && ok; tap++, k_col += p.C) {
+                        for (int wp = 1; wp >= 0; wp--) {  // per tap: the low weight plane's block, then the high one's
                             if (!mbar_wait(empty_a(s), ph ^ 1u)) {
                                 conv_timeout(p.status, 21);
                                 ok = false;
@@ -513,13 +513,15 @@ __global__ void __launch_bounds__(kHaloThreads, 1)
                         if (!mbar_wait(wp ? full_h(hs) : full_h(hs_lo), wp ? hph : hph_lo)) {
                             conv_timeout(p.status, 26);
                             ok = false;
-                            break;
                         }
-                        tc_fence_after();
-                        uint64_t row_hi = h_desc0 + uint64_t(hs * (halo_bytes >> 4)), row_lo = h_desc0 + uint64_t(hs_lo * (halo_bytes >> 4));
-                        for (int ky = 0; ky < p.kh && ok; ky++, row_hi += (64 * 128) >> 4, row_lo += (64 * 128) >> 4) {
-                            uint64_t b_hi = row_hi, b_lo = row_lo;
-                            for (int kx = 0; kx < p.kw; kx++, b_hi += 128 >> 4, b_lo += 128 >> 4) {
+                    }
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint64_t row_hi = h_desc0 + uint64_t(hs * (halo_bytes >> 4)), row_lo = h_desc0 + uint64_t(hs_lo * (halo_bytes >> 4));
+                    for (int ky = 0; ky < p.kh && ok; ky++, row_hi += (64 * 128) >> 4, row_lo += (64 * 128) >> 4) {
+                        uint64_t b_hi = row_hi, b_lo = row_lo;
+                        for (int kx = 0; kx < p.kw && ok; kx++, b_hi += 128 >> 4, b_lo += 128 >> 4) {
+                            for (int wp = 1; wp >= 0; wp--) {
                                 if (!mbar_wait(full_a(s), ph)) {
                                     conv_timeout(p.status, 23);
                                     ok = false;
