@@ -909,15 +909,21 @@ __global__ void __launch_bounds__(320, 1)
             constexpr uint32_t idesc_qk = make_idesc(kBQ, kBKV, IS_BF16 ? 1 : 0, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc(kBQ, D, IS_BF16 ? 1 : 0, 0, 1);
             bool ok = true;
-            uint32_t ring_base = 0;                        // ring entries consumed by earlier items
             uint32_t q_use[2] = {0, 0}, p_cnt[2] = {0, 0};  // items with tile t active / P_t blocks consumed so far
-            auto slot_of = [&](int i) { return int((ring_base + uint32_t(i)) % uint32_t(NS)); };
-            auto wait_slot = [&](int i) -> uint32_t {  // returns the slot base, 0 on timeout
-                const uint32_t g = ring_base + uint32_t(i);
-                const int s = int(g % uint32_t(NS));
-                if (!mbar_wait(kv_full(s), (g / uint32_t(NS)) & 1u)) { attn_timeout(p.status, 32); ok = false; return 0u; }
+            // The ring's entries are consumed strictly in the order they were produced (K of block 0, then V of block j and K
+            // of block j + 1 for every j), across items: the next entry's slot and phase are kept as a counter, not derived
+            // from the entry number by divisions (scalar work of this one thread sits on the tensor pipe's critical path).
+            uint32_t rs = 0, rph = 0;
+            auto take_slot = [&](uint32_t& idx) -> uint32_t {  // waits for the next entry: its slot index, and its base (0 on timeout)
+                idx = rs;
+                if (!mbar_wait(kv_full(int(rs)), rph)) { attn_timeout(p.status, 32); ok = false; return 0u; }
                 tc_fence_after();
-                return sKV + uint32_t(s) * kTile;
+                const uint32_t slot_base = sKV + rs * kTile;
+                if (++rs == uint32_t(NS)) {
+                    rs = 0;
+                    rph ^= 1u;
+                }
+                return slot_base;
             };
             // Q K^T of tile t: hi*hi, plus the two cross terms for fp32 operands (small terms first)
             // Descriptors are built once per operand tile; the k-steps only add a constant to the address
@@ -952,30 +958,30 @@ __global__ void __launch_bounds__(320, 1)
                 if (!mbar_wait(q_full(t), q_use[t] & 1u)) { attn_timeout(p.status, 33); ok = false; }
             }
             if (ok) {
-                const uint32_t k_hi = wait_slot(0);
-                const uint32_t k_lo = (SPLIT && ok) ? wait_slot(1) : 0u;
+                uint32_t i_k0 = 0, i_k1 = 0;
+                const uint32_t k_hi = take_slot(i_k0);
+                const uint32_t k_lo = (SPLIT && ok) ? take_slot(i_k1) : 0u;
                 if (ok) {
                     for (int t = 0; t < 2; t++) {
                         if (nb[t] == 0) continue;
                         issue_qk(t, k_hi, k_lo);
                         if (nb[t] == 1) umma_commit(q_empty(t));  // that was this item's last read of Q_t
                     }
-                    umma_commit(kv_empty(slot_of(0)));
-                    if (SPLIT) umma_commit(kv_empty(slot_of(1)));
+                    umma_commit(kv_empty(int(i_k0)));
+                    if (SPLIT) umma_commit(kv_empty(int(i_k1)));
                 }
             }
             for (int j = 0; j < n_max && ok; j++) {
-                const int iv = EB * j + (SPLIT ? 2 : 1);      // first V entry of block j
-                const int ik = EB * (j + 1);                  // first K entry of block j+1
-                const uint32_t v_hi = wait_slot(iv);
+                uint32_t i_v0 = 0, i_v1 = 0, i_k0 = 0, i_k1 = 0;  // slots of V of block j and K of block j + 1
+                const uint32_t v_hi = take_slot(i_v0);
                 if (!ok) break;
-                const uint32_t v_lo = SPLIT ? wait_slot(iv + 1) : 0u;
+                const uint32_t v_lo = SPLIT ? take_slot(i_v1) : 0u;
                 if (!ok) break;
                 uint32_t k_hi = 0, k_lo = 0;
                 if (j + 1 < n_max) {
-                    k_hi = wait_slot(ik);
+                    k_hi = take_slot(i_k0);
                     if (!ok) break;
-                    if (SPLIT) k_lo = wait_slot(ik + 1);
+                    if (SPLIT) k_lo = take_slot(i_k1);
                     if (!ok) break;
                 }
                 for (int t = 0; t < 2 && ok; t++) {
@@ -1009,14 +1015,13 @@ __global__ void __launch_bounds__(320, 1)
                     }
                 }
                 if (!ok) break;
-                umma_commit(kv_empty(slot_of(iv)));
-                if (SPLIT) umma_commit(kv_empty(slot_of(iv + 1)));
+                umma_commit(kv_empty(int(i_v0)));
+                if (SPLIT) umma_commit(kv_empty(int(i_v1)));
                 if (j + 1 < n_max) {
-                    umma_commit(kv_empty(slot_of(ik)));
-                    if (SPLIT) umma_commit(kv_empty(slot_of(ik + 1)));
+                    umma_commit(kv_empty(int(i_k0)));
+                    if (SPLIT) umma_commit(kv_empty(int(i_k1)));
                 }
             }
-            ring_base += uint32_t(EB * n_max);
             for (int t = 0; t < 2; t++) if (nb[t] > 0) q_use[t]++;
           }
         }
